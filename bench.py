@@ -1,0 +1,385 @@
+#!/usr/bin/env python
+"""Benchmark of the B200 hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+One process per GPU (for N > 1 launch with torch.distributed.run; rank, local
+rank and world size come from the environment).  A step is one pass of the
+workload over one batch of seeded synthetic input.  W warm-up steps, then exactly
+K steps timed with CUDA events on the launching stream between a barrier +
+synchronize on both sides; the time is the max over ranks; rank 0 prints ONE
+JSON line.
+
+Workloads
+  segops   segmented wave64 reduce + inclusive-scan sweep over 2^26 elements per
+           dtype: reduce {f32,f64,i32,i64} x {sum,max,min}, reduce {f16,bf16} sum
+           (fp32 accumulation), scan-sum {f32,f64,i32,i64,f16,bf16}.  HBM-bound.
+           N > 1: every rank sweeps its own 2^26-element shard (weak scaling).
+
+--impl reference times the CPU statement of the same path (the oracle) on the
+host cores, on a bounded sample, in the same metric.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def load_peaks():
+    """Measured roofline denominators (driver-written file), else the stated fallback."""
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return {"hbm_gbs": float(p["hbm_gbs"]), "bf16_tflops": float(p["bf16_tflops"]),
+                "bf16_tflops_sustained": float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+# --------------------------------------------------------------------------------------
+# clocks: sampled DURING the timed region through NVML (read-only)
+# --------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
+               0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, index: int, period: float = 0.01):
+        self.index, self.period = index, period
+        self.samples, self.reasons = [], set()
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self.h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self.nv = None
+
+    def _run(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)))
+                bits = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h))
+                for b, name in self.REASONS.items():
+                    if bits & b:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------------------
+# workload: segmented reduce / scan sweep
+# --------------------------------------------------------------------------------------
+class SegopsSweep:
+    name = "segops"
+    metric = "segmented wave64 reduce+scan sweep throughput (algorithmic bytes)"
+    unit = "GB/s"
+    dtype = "f32,f64,i32,i64 (+f16,bf16 with f32 accumulation)"
+    N = 1 << 26
+
+    KINDS = ["f32", "f64", "i32", "i64", "f16", "bf16"]
+    SIZE = {"f32": 4, "f64": 8, "i32": 4, "i64": 8, "f16": 2, "bf16": 2}
+
+    def __init__(self, n=None):
+        self.n = n or self.N
+        self.cases = []   # (label, fn, kind, op, bytes)
+        for kind in ("f32", "f64", "i32", "i64"):
+            for op in ("sum", "max", "min"):
+                self.cases.append((f"reduce_{op}<{kind}>", "reduce", kind, op, self.n * self.SIZE[kind] + self.n // 64 * self.SIZE[kind]))
+        for kind in ("f16", "bf16"):
+            self.cases.append((f"reduce_sum<{kind}>", "reduce", kind, "sum", self.n * 2 + self.n // 64 * 4))
+        for kind in self.KINDS:
+            self.cases.append((f"scan_inclusive_sum<{kind}>", "scan", kind, "sum", 2 * self.n * self.SIZE[kind]))
+        self.bytes_per_step = sum(c[4] for c in self.cases)
+
+    def config(self, world):
+        return {"workload": "segmented wave64 reduce + inclusive-scan sweep (BASELINE config 2)",
+                "elements_per_dtype_per_gpu": self.n, "segment": 64,
+                "launches_per_step": len(self.cases),
+                "sharding": f"segments x{world}, no collective",
+                "l2": "inputs larger than L2; successive launches read different buffers",
+                "inputs": "f32/f64 N(0,1); i32/i64 U[-1000,1000]; f16/bf16 N(0,1) rounded; seeded"}
+
+    # host inputs (pinned) -- seeded; rank shifts the seed so shards differ
+    def make_host(self, torch, rank, pinned=True):
+        import numpy as np
+        rng = np.random.default_rng(0xB200 + 2 + 1000 * rank)
+        host = {}
+        for kind in self.KINDS:
+            if kind in ("i32", "i64"):
+                a = rng.integers(-1000, 1001, self.n, dtype=np.int32 if kind == "i32" else np.int64)
+                t = torch.from_numpy(a)
+            else:
+                a = rng.standard_normal(self.n, dtype=np.float32)
+                t = torch.from_numpy(a)
+                if kind == "f64":
+                    t = t.double()
+                elif kind == "f16":
+                    t = t.half()
+                elif kind == "bf16":
+                    t = t.bfloat16()
+            host[kind] = t.pin_memory() if pinned else t
+        return host
+
+    def setup(self, torch, pkg, device, rank):
+        self.torch, self.pkg = torch, pkg
+        self.host = self.make_host(torch, rank)
+        self.dev = {k: v.to(device, non_blocking=True) for k, v in self.host.items()}
+        self.out = []
+        for label, fn, kind, op, _ in self.cases:
+            x = self.dev[kind]
+            if fn == "reduce":
+                odt = torch.float32 if kind in ("f16", "bf16") else x.dtype
+                self.out.append(torch.empty(self.n // 64, dtype=odt, device=device))
+            else:
+                self.out.append(torch.empty_like(x))
+        self.host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in self.out]
+        torch.cuda.synchronize()
+
+    def step(self, events=None):
+        """One sweep with inputs resident in HBM.  events: list that receives one
+        CUDA event after every launch (plus one before the first)."""
+        torch, pkg = self.torch, self.pkg
+        for i, (label, fn, kind, op, _) in enumerate(self.cases):
+            if fn == "reduce":
+                pkg.segreduce(self.dev[kind], op, out=self.out[i])
+            else:
+                pkg.segscan(self.dev[kind], op, out=self.out[i])
+            if events is not None:
+                e = torch.cuda.Event(enable_timing=True)
+                e.record()
+                events.append(e)
+
+    def step_e2e(self):
+        """The same sweep through the public API from HOST buffers: H2D of every
+        input from pinned memory, the launches, D2H of every result."""
+        for k, h in self.host.items():
+            self.dev[k].copy_(h, non_blocking=True)
+        self.step()
+        for o, h in zip(self.out, self.host_out):
+            h.copy_(o, non_blocking=True)
+
+    def e2e_bytes(self):
+        h2d = sum(v.numel() * v.element_size() for v in self.host.values())
+        d2h = sum(v.numel() * v.element_size() for v in self.host_out)
+        return h2d, d2h
+
+    # CPU statement of the same sweep on a bounded sample
+    def cpu_run(self, orc, n, threads, reps=1):
+        import numpy as np
+        rng = np.random.default_rng(0xB200 + 2)
+        f32 = rng.standard_normal(n, dtype=np.float32)
+        data = {"f32": f32, "f64": f32.astype(np.float64),
+                "i32": rng.integers(-1000, 1001, n, dtype=np.int32), "i64": rng.integers(-1000, 1001, n, dtype=np.int64),
+                "f16": orc.f32_to_f16_bits(f32), "bf16": orc.f32_to_bf16_bits(f32)}
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            for label, fn, kind, op, _b in self.cases:
+                o = orc.OPS[op]
+                if kind in ("f16", "bf16"):
+                    if fn == "reduce":
+                        orc.shfl_reduce_narrow(o, data[kind], kind == "bf16", threads=threads)
+                    else:
+                        orc.shfl_scan_narrow(o, data[kind], kind == "bf16", threads=threads)
+                elif fn == "reduce":
+                    orc.seq_reduce(o, data[kind], threads=threads)
+                else:
+                    orc.seq_scan(o, data[kind], threads=threads)
+        dt = (time.perf_counter() - t0) / reps
+        scale = n / self.n
+        return self.bytes_per_step * scale / dt / 1e9, dt
+
+
+WORKLOADS = {"segops": SegopsSweep}
+
+
+# --------------------------------------------------------------------------------------
+def reference_arm(args, wl, rank, world):
+    """The CPU statement of the path (oracle) on the host cores; rank 0 only."""
+    if rank != 0:
+        return
+    import oracle as orc
+    threads = orc.hardware_threads()
+    sample_n = 1 << 24
+    for _ in range(max(1, args.warmup if args.warmup < 3 else 1)):
+        wl.cpu_run(orc, 1 << 20, threads)
+    vals = []
+    t_all = time.perf_counter()
+    for _ in range(args.steps):
+        v, dt = wl.cpu_run(orc, sample_n, threads)
+        vals.append((v, dt))
+        if time.perf_counter() - t_all > 120:
+            break
+    v = statistics.median(x[0] for x in vals)
+    ms = statistics.median(x[1] for x in vals) * 1e3
+    line = {"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus,
+            "steps": len(vals), "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)",
+            "config": wl.config(world),
+            "cpu_baseline": {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
+                             "sample": f"the same sweep over 2^24 elements per dtype (1/4 of the workload) per step; "
+                                       f"sequential per-segment loops, segments split over {threads} host threads"},
+            "e2e": {"value": v, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="segops", choices=sorted(WORKLOADS))
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer (end-to-end) measurement")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--elements", type=int, default=None,
+                    help="elements per dtype (default 2^26); smaller cases are for profiler captures only")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    wl = WORKLOADS[args.workload](args.elements) if args.elements else WORKLOADS[args.workload]()
+
+    if args.impl == "reference":
+        reference_arm(args, wl, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    pkg.lib()                                   # fail loudly if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    peaks = load_peaks()
+    wl.setup(torch, pkg, device, rank)
+    warm = max(args.warmup, 3)
+    for _ in range(warm):
+        wl.step()
+    barrier()
+
+    # ---- device-resident timing, one event after every launch -------------------------
+    events = []
+    launches0 = pkg.launch_count()
+    with ClockSampler(local_rank) as clk:
+        barrier()
+        start = torch.cuda.Event(enable_timing=True)
+        start.record()
+        events.append(start)
+        for _ in range(args.steps):
+            wl.step(events)
+        barrier()
+    launches = pkg.launch_count() - launches0
+    total_ms = events[0].elapsed_time(events[-1])
+    t = torch.tensor([total_ms], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms = float(t.item())
+    ms_per_step = total_ms / args.steps
+    value = world * wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9
+
+    # per-kernel durations (average over the timed steps)
+    ncase = len(wl.cases)
+    per = [0.0] * ncase
+    for s in range(args.steps):
+        for i in range(ncase):
+            per[i] += events[s * ncase + i].elapsed_time(events[s * ncase + i + 1])
+    kernels = []
+    for i, (label, fn, kind, op, nbytes) in enumerate(wl.cases):
+        us = per[i] / args.steps * 1e3
+        gbs = nbytes / (us * 1e-6) / 1e9
+        kernels.append({"kernel": label, "us": round(us, 2), "bytes": nbytes, "GB/s": round(gbs, 1),
+                        "frac": round(gbs / peaks["hbm_gbs"], 4)})
+    dom = max(range(ncase), key=lambda i: per[i])
+    roofline = {"bound": "hbm", "kernel": kernels[dom]["kernel"], "achieved": kernels[dom]["GB/s"],
+                "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": kernels[dom]["frac"],
+                "peak_source": f"{peaks['source']} copy bandwidth", "traffic": TRAFFIC.get(kernels[dom]["kernel"])}
+
+    # ---- end to end: host buffers in, host results out, every step ----------------------
+    e2e_steps = args.e2e_steps or max(3, min(args.steps, 10))
+    wl.step_e2e()
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(e2e_steps):
+        wl.step_e2e()
+    e1.record()
+    barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    e2e_ms = float(t.item()) / e2e_steps
+    h2d, d2h = wl.e2e_bytes()
+    e2e = {"value": world * wl.bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": wl.unit, "ms_per_step": e2e_ms,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps}
+
+    # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------
+    cpu = None
+    if rank == 0 and world == 1 and not args.no_cpu_baseline:
+        import oracle as orc
+        threads = orc.hardware_threads()
+        wl.cpu_run(orc, 1 << 20, threads)
+        v, dt = wl.cpu_run(orc, 1 << 24, threads, reps=3)
+        cpu = {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
+               "sample": f"the same sweep over 2^24 elements per dtype (1/4 of the workload), 3 repetitions, "
+                         f"{dt:.2f} s each; sequential per-segment loops, segments split over {threads} host threads"}
+
+    if rank == 0:
+        line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+                "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+                "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)", "config": wl.config(world),
+                "clocks": clk.summary(), "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
+                "cpu_baseline": cpu, "kernels": kernels}
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
+# captures summarised under profiles/; filled in as captures are taken.
+TRAFFIC = {}
+
+if __name__ == "__main__":
+    main()
