@@ -32,7 +32,18 @@ SYMBOLS = {
     "b200p_segscan_inclusive": (_i, [_i, _i, _vp, _vp, _sz, _vp]),
     "b200p_segscan_exclusive_sum": (_i, [_i, _vp, _vp, _sz, _vp]),
     "b200p_wave_probe": (_i, [_i, _i, _i, _vp, _vp, _vp]),
+    "b200p_attn_decode_workspace_bytes": (_sz, [_vp]),
+    "b200p_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "b200p_attn_decode_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
+    "b200p_attn_merge_lse": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "b200p_attn_workspace_status": (_i, [_vp, _vp]),
 }
+
+
+class DecodeArgs(C.Structure):
+    """struct b200p_decode_args (include/b200p.h)."""
+    _fields_ = [("D", _i), ("N", _i), ("nQHeads", _i), ("nKVHeads", _i), ("stride_kv", _i), ("batch", _i),
+                ("dtype", _i), ("kv_batch_stride", _ll), ("key_offset", _ll)]
 
 
 class B200PError(RuntimeError):
@@ -136,3 +147,78 @@ def wave_probe(x64, fn: str = "reduce", op: str = "sum"):
     code = {"reduce": 0, "scan": 1, "scan_exclusive": 2}[fn]
     _check(lib().b200p_wave_probe(code, OPS[op], _dtype_code(x64), x64.data_ptr(), out.data_ptr(), _stream(x64)), "wave_probe")
     return out
+
+
+# ---- decode attention (cdna3::attn::decode / decode_dme) ----------------------------------
+def _decode_args(q, K, N, key_offset):
+    """q [batch, nQH, D] (or [nQH, D]); K/V [batch, nKVH, stride_kv, D] (or [nKVH, stride_kv, D])."""
+    if q.dim() == 2:
+        q = q.unsqueeze(0)
+    if K.dim() == 3:
+        K = K.unsqueeze(0)
+    batch, nQH, D = q.shape
+    _, nKVH, stride_kv, _ = K.shape
+    N = stride_kv - key_offset if N is None else N
+    a = DecodeArgs(D, N, nQH, nKVH, stride_kv, batch, _dtype_code(q), K.stride(0), key_offset)
+    return a, batch, nQH, D
+
+
+def decode_workspace(q, K, N=None, key_offset: int = 0):
+    """Scratch tensor of the size the decode launch needs for these shapes."""
+    import torch
+    a, *_ = _decode_args(q, K, N, key_offset)
+    nbytes = int(lib().b200p_attn_decode_workspace_bytes(C.byref(a)))
+    if nbytes == 0:
+        raise B200PError(-6, "decode_workspace")
+    return torch.empty(nbytes, dtype=torch.uint8, device=q.device)
+
+
+def decode(q, K, V, N=None, out=None, workspace=None, key_offset: int = 0):
+    """One query token per sequence against N cached keys.  K/V may be the packed
+    [.., N, D] tensors of cdna3::attn::decode or the strided cache [.., max_seq, D]
+    of cdna3::attn::decode_dme (then pass N)."""
+    import torch
+    for t, n in ((q, "q"), (K, "K"), (V, "V")):
+        _dev(t, n)
+    a, batch, nQH, D = _decode_args(q, K, N, key_offset)
+    ws = decode_workspace(q, K, N, key_offset) if workspace is None else workspace
+    if out is None:
+        out = torch.empty_like(q)
+    _check(lib().b200p_attn_decode(q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), C.byref(a),
+                                   ws.data_ptr(), ws.numel(), _stream(q)), "attn_decode")
+    return out
+
+
+def decode_partial(q, K, V, N=None, workspace=None, key_offset: int = 0, out=None, lse=None):
+    """Attention over a shard of the KV sequence: (O normalised over the shard as fp32
+    [batch, nQH, D], lse [batch, nQH]) for merge_lse."""
+    import torch
+    for t, n in ((q, "q"), (K, "K"), (V, "V")):
+        _dev(t, n)
+    a, batch, nQH, D = _decode_args(q, K, N, key_offset)
+    ws = decode_workspace(q, K, N, key_offset) if workspace is None else workspace
+    if out is None:
+        out = torch.empty((batch, nQH, D), dtype=torch.float32, device=q.device)
+    if lse is None:
+        lse = torch.empty((batch, nQH), dtype=torch.float32, device=q.device)
+    _check(lib().b200p_attn_decode_partial(q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), lse.data_ptr(),
+                                           C.byref(a), ws.data_ptr(), ws.numel(), _stream(q)), "attn_decode_partial")
+    return out, lse
+
+
+def merge_lse(o_parts, lse_parts, dtype, out=None):
+    """o_parts [parts, rows.., D] fp32, lse_parts [parts, rows..] -> [rows.., D] in dtype."""
+    import torch
+    _dev(o_parts, "o_parts"); _dev(lse_parts, "lse_parts")
+    parts, D = o_parts.shape[0], o_parts.shape[-1]
+    rows = lse_parts[0].numel()
+    if out is None:
+        out = torch.empty(o_parts.shape[1:], dtype=dtype, device=o_parts.device)
+    _check(lib().b200p_attn_merge_lse(o_parts.data_ptr(), lse_parts.data_ptr(), parts, rows, D, _dtype_code(out),
+                                      out.data_ptr(), _stream(o_parts)), "attn_merge_lse")
+    return out
+
+
+def workspace_status(workspace) -> int:
+    """0, or B200P_E_TIMEOUT if a kernel using this workspace abandoned a bounded wait (synchronises)."""
+    return int(lib().b200p_attn_workspace_status(workspace.data_ptr(), _stream(workspace)))

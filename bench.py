@@ -190,6 +190,9 @@ class SegopsSweep:
         for o, h in zip(self.out, self.host_out):
             h.copy_(o, non_blocking=True)
 
+    cpu_sample = 1 << 24
+    cpu_sample_text = "the same sweep over 2^24 elements per dtype (1/4 of the workload)"
+
     def e2e_bytes(self):
         h2d = sum(v.numel() * v.element_size() for v in self.host.values())
         d2h = sum(v.numel() * v.element_size() for v in self.host_out)
@@ -221,7 +224,71 @@ class SegopsSweep:
         return self.bytes_per_step * scale / dt / 1e9, dt
 
 
-WORKLOADS = {"segops": SegopsSweep}
+# --------------------------------------------------------------------------------------
+# workload: GQA decode (BASELINE config 4)
+# --------------------------------------------------------------------------------------
+class DecodeGQA:
+    name = "decode"
+    metric = "GQA decode attention throughput (algorithmic K/V/q/o bytes)"
+    unit = "GB/s"
+    dtype = "bf16 (fp32 softmax and accumulation)"
+    B, NQH, NKVH, D, N = 64, 32, 8, 128, 8192
+
+    def __init__(self, n=None):
+        if n:
+            self.N = n
+        self.bytes_per_step = 2 * self.B * self.NKVH * self.N * self.D * 2 + 2 * self.B * self.NQH * self.D * 2
+        self.cases = [("decode_splitkv_kernel (+ combine)", None, None, None, self.bytes_per_step)]
+
+    def config(self, world):
+        return {"workload": "GQA decode (BASELINE config 4)", "batch_per_gpu": self.B, "q_heads": self.NQH, "kv_heads": self.NKVH,
+                "head_dim": self.D, "kv_len": self.N, "sharding": f"(batch, kv-head) x{world}, no collective",
+                "l2": "K/V (2 GiB) larger than L2", "e2e": "q H2D + o D2H every step; the KV cache is resident state",
+                "inputs": "q, K, V ~ N(0,1) rounded to bf16, seeded"}
+
+    def setup(self, torch, pkg, device, rank):
+        self.torch, self.pkg = torch, pkg
+        g = torch.Generator(device=device); g.manual_seed(0xB204 + 1000 * rank)
+        self.q = torch.randn(self.B, self.NQH, self.D, device=device, generator=g).bfloat16()
+        self.K = torch.randn(self.B, self.NKVH, self.N, self.D, device=device, generator=g).bfloat16()
+        self.V = torch.randn(self.B, self.NKVH, self.N, self.D, device=device, generator=g).bfloat16()
+        self.o = torch.empty_like(self.q)
+        self.ws = pkg.decode_workspace(self.q, self.K)
+        self.q_host = self.q.cpu().pin_memory()
+        self.o_host = torch.empty(self.o.shape, dtype=self.o.dtype).pin_memory()
+        torch.cuda.synchronize()
+
+    def step(self, events=None):
+        self.pkg.decode(self.q, self.K, self.V, out=self.o, workspace=self.ws)
+        if events is not None:
+            e = self.torch.cuda.Event(enable_timing=True); e.record(); events.append(e)
+
+    def step_e2e(self):
+        self.q.copy_(self.q_host, non_blocking=True)
+        self.step()
+        self.o_host.copy_(self.o, non_blocking=True)
+
+    def e2e_bytes(self):
+        return self.q_host.numel() * 2, self.o_host.numel() * 2
+
+    def cpu_run(self, orc, n, threads, reps=1):
+        """n = sequences of the batch (full kv length)."""
+        import numpy as np
+        rng = np.random.default_rng(0xB204)
+        q = rng.standard_normal((n, self.NQH, self.D), dtype=np.float32)
+        K = rng.standard_normal((n, self.NKVH, self.N, self.D), dtype=np.float32)
+        V = rng.standard_normal((n, self.NKVH, self.N, self.D), dtype=np.float32)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            orc.cpu_decode(q, K, V, self.D, self.N, self.NQH, self.NKVH, batch=n, threads=threads)
+        dt = (time.perf_counter() - t0) / reps
+        return self.bytes_per_step * (n / self.B) / dt / 1e9, dt
+
+    cpu_sample = 8
+    cpu_sample_text = "8 of the 64 sequences at full KV length"
+
+
+WORKLOADS = {"segops": SegopsSweep, "decode": DecodeGQA}
 
 
 # --------------------------------------------------------------------------------------
@@ -231,9 +298,8 @@ def reference_arm(args, wl, rank, world):
         return
     import oracle as orc
     threads = orc.hardware_threads()
-    sample_n = 1 << 24
-    for _ in range(max(1, args.warmup if args.warmup < 3 else 1)):
-        wl.cpu_run(orc, 1 << 20, threads)
+    sample_n = wl.cpu_sample
+    wl.cpu_run(orc, max(1, sample_n // 8), threads)
     vals = []
     t_all = time.perf_counter()
     for _ in range(args.steps):
@@ -248,8 +314,7 @@ def reference_arm(args, wl, rank, world):
             "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)",
             "config": wl.config(world),
             "cpu_baseline": {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
-                             "sample": f"the same sweep over 2^24 elements per dtype (1/4 of the workload) per step; "
-                                       f"sequential per-segment loops, segments split over {threads} host threads"},
+                             "sample": f"{wl.cpu_sample_text} per step; independent units split over {threads} host threads"},
             "e2e": {"value": v, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
     print(json.dumps(line), flush=True)
 
@@ -328,7 +393,7 @@ def main():
             per[i] += events[s * ncase + i].elapsed_time(events[s * ncase + i + 1])
     kernels = []
     for i, (label, fn, kind, op, nbytes) in enumerate(wl.cases):
-        us = per[i] / args.steps * 1e3
+        us = max(per[i] / args.steps * 1e3, 1e-3)
         gbs = nbytes / (us * 1e-6) / 1e9
         kernels.append({"kernel": label, "us": round(us, 2), "bytes": nbytes, "GB/s": round(gbs, 1),
                         "frac": round(gbs / peaks["hbm_gbs"], 4)})
@@ -360,11 +425,10 @@ def main():
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle as orc
         threads = orc.hardware_threads()
-        wl.cpu_run(orc, 1 << 20, threads)
-        v, dt = wl.cpu_run(orc, 1 << 24, threads, reps=3)
+        wl.cpu_run(orc, max(1, wl.cpu_sample // 8), threads)
+        v, dt = wl.cpu_run(orc, wl.cpu_sample, threads, reps=3)
         cpu = {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
-               "sample": f"the same sweep over 2^24 elements per dtype (1/4 of the workload), 3 repetitions, "
-                         f"{dt:.2f} s each; sequential per-segment loops, segments split over {threads} host threads"}
+               "sample": f"{wl.cpu_sample_text}, 3 repetitions, {dt:.2f} s each; independent units split over {threads} host threads"}
 
     if rank == 0:
         line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,

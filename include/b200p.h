@@ -94,6 +94,69 @@ int b200p_segscan_exclusive_sum(int dtype, const void* in, void* out,
 int b200p_wave_probe(int fn, int op, int dtype, const void* in64, void* out64,
                      b200p_stream_t stream);
 
+/* =========================================================================
+ * FA2 attention.
+ * Layouts are the reference's (cdna3-prims/include/cdna3/attention.hpp:83-85,
+ * 112-116, 146-148): Q,O [batch, nQH, seqQ, D]; K,V [batch, nKVH, seqK, D];
+ * decode q,o [nQH, D] and K,V [nKVH, N, D] or the strided cache
+ * [nKVH, max_seq, D]; nQH % nKVH == 0; scale fixed at 1/sqrt(D); 16-bit I/O,
+ * fp32 softmax and accumulation.  dtype is B200P_F16 (the reference's type) or
+ * B200P_BF16.
+ * ========================================================================= */
+
+/* Decode arguments.  The first four fields are cdna3::attn::DecodeCfg
+ * (attention.hpp:73-78), stride_kv is DecodeDmeCfg::stride_kv
+ * (cdna3-prims/include/cdna3/detail/fa_decode_dme_kernel.hpp:45-48); the rest
+ * extends the reference's single sequence to a batch and to a shard of the
+ * KV sequence. */
+typedef struct b200p_decode_args {
+    int D;                     /* head dimension: 64 or 128                               */
+    int N;                     /* number of cached keys attended to                       */
+    int nQHeads;
+    int nKVHeads;
+    int stride_kv;             /* keys between consecutive KV heads: N if packed, max_seq
+                                  for the cache layout                                    */
+    int batch;                 /* sequences; q,o are [batch, nQH, D] (reference: 1)       */
+    int dtype;                 /* B200P_F16 or B200P_BF16                                 */
+    long long kv_batch_stride; /* elements between sequences in K and V;
+                                  0 = nKVHeads * stride_kv * D                            */
+    long long key_offset;      /* first key of each head to attend to (a KV shard starts
+                                  here); N keys are read from it                          */
+} b200p_decode_args;
+
+/* Bytes of caller-owned scratch the decode entry points need for these
+ * arguments (split-KV partials + a status word); 0 for invalid arguments.
+ * The launchers allocate nothing, like the reference's (attention.hpp:117-137). */
+size_t b200p_attn_decode_workspace_bytes(const b200p_decode_args* args);
+
+/* Stands in for cdna3::attn::decode (attention.hpp:117-137, packed K/V:
+ * stride_kv = N) and cdna3::attn::decode_dme (attention.hpp:152-173, strided
+ * cache: stride_kv = max_seq).  workspace: 256-byte aligned device memory of at
+ * least b200p_attn_decode_workspace_bytes(args). */
+int b200p_attn_decode(const void* q, const void* K, const void* V, void* o,
+                      const b200p_decode_args* args, void* workspace, size_t workspace_bytes,
+                      b200p_stream_t stream);
+
+/* The same attention over a shard of the KV sequence, returning what the
+ * cross-shard combine needs: o_f32 [batch, nQH, D] normalised over the shard and
+ * lse [batch, nQH] (natural log of the shard's softmax denominator, including
+ * the running max).  No counterpart in the reference, which is single-GPU; the
+ * merge it feeds is the reference's split-KV merge
+ * (cdna3-prims/include/cdna3/detail/fa_decode_kernel.hpp:75-92). */
+int b200p_attn_decode_partial(const void* q, const void* K, const void* V, float* o_f32, float* lse,
+                              const b200p_decode_args* args, void* workspace, size_t workspace_bytes,
+                              b200p_stream_t stream);
+
+/* Merge `parts` shard results: o_parts [parts, rows, D] fp32, lse_parts
+ * [parts, rows] -> o [rows, D] in `dtype`.
+ * O = sum_g e^{lse_g-M} O_g / sum_g e^{lse_g-M} (fa_decode_kernel.hpp:75-92). */
+int b200p_attn_merge_lse(const float* o_parts, const float* lse_parts, int parts, int rows, int D,
+                         int dtype, void* o, b200p_stream_t stream);
+
+/* Synchronises `stream` and reports whether a kernel that used `workspace`
+ * abandoned a bounded wait (B200P_E_TIMEOUT) or not (0). */
+int b200p_attn_workspace_status(const void* workspace, b200p_stream_t stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,133 @@
+// ---------------------------------------------------------------------------
+// dme/dme_tma.cuh -- asynchronous global -> shared tile copies for sm_100a.
+//
+// Plays the role of the reference's dme-abstraction headers
+//   research/dme-abstraction/include/dme/dme_copy.hpp:77-94,133-146
+//     (copy_element_stream / copy_tile_1d_stream / wait)
+//   research/dme-abstraction/include/dme/tensor_prefetch.hpp:64-79,151-196
+//     (prefetch_tile2d_fp16 / AsyncTile2D ping-pong)
+// The reference issues one 4-byte global_load_lds per lane and waits with
+// s_waitcnt; here ONE elected thread hands a whole contiguous tile to the TMA
+// engine (cp.async.bulk) and completion is signalled through an mbarrier that
+// the consumers poll, so any number of stages can be in flight.
+//
+// Every wait is BOUNDED: wait() returns false after kSpinLimit polls instead of
+// spinning for ever, so a lost copy turns into an error status, not a hang.
+//
+// Alignment: source, destination and byte count of a bulk copy must be
+// multiples of 16 bytes.  No multicast form is used anywhere.
+// ---------------------------------------------------------------------------
+#pragma once
+#include <cuda_runtime.h>
+#include <cstdint>
+
+namespace dme {
+
+constexpr uint32_t kSpinLimit = 1u << 24;   // polls; try_wait itself blocks for a while per poll
+
+__device__ __forceinline__ uint32_t smem_addr(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+// ---- mbarrier --------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t arrivals) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(smem_addr(bar)), "r"(arrivals) : "memory");
+}
+// Make freshly initialised barriers visible to the async proxy (call once, by
+// the initialising thread, before the CTA-wide barrier that publishes them).
+__device__ __forceinline__ void mbar_init_fence() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(smem_addr(bar)) : "memory");
+}
+// Arrive and announce `bytes` of asynchronous copies that will complete on this barrier.
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" :: "r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait for the phase with the given parity.  false = gave up.
+__device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity) {
+    for (uint32_t i = 0; i < kSpinLimit; ++i)
+        if (mbar_try_wait(bar, parity)) return true;
+    return false;
+}
+
+// ---- L2 policy for data that is read exactly once -------------------------------------
+__device__ __forceinline__ uint64_t policy_evict_first() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+__device__ __forceinline__ uint64_t policy_evict_last() {
+    uint64_t p;
+    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+    return p;
+}
+
+// ---- copies (issued by ONE thread) -----------------------------------------------------
+// Contiguous `bytes` from global to shared; completion adds `bytes` to `bar`'s
+// transaction count.  The streaming form marks the lines evict-first in L2
+// (the reference's sc0 "streaming" hint, dme_copy.hpp:77-86).
+__device__ __forceinline__ void copy_tile_1d(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 :: "r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void copy_tile_1d_stream(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar,
+                                                    uint64_t policy) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1], %2, [%3], %4;"
+                 :: "r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy) : "memory");
+}
+
+// Tiled 2-D tensor-map copy: box at element coordinates (x, y); x * element size
+// must be a multiple of 16 bytes.
+__device__ __forceinline__ void copy_tile_2d(void* smem_dst, const void* tensor_map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(smem_addr(smem_dst)), "l"(tensor_map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void copy_tile_3d(void* smem_dst, const void* tensor_map, int x, int y, int z, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 :: "r"(smem_addr(smem_dst)), "l"(tensor_map), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(z) : "memory");
+}
+__device__ __forceinline__ void copy_tile_4d(void* smem_dst, const void* tensor_map, int x, int y, int z, int w, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+                 :: "r"(smem_addr(smem_dst)), "l"(tensor_map), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
+// Streaming form: lines are marked evict-first in L2 (data read exactly once).
+__device__ __forceinline__ void copy_tile_4d_stream(void* smem_dst, const void* tensor_map, int x, int y, int z, int w,
+                                                    uint64_t* bar, uint64_t policy) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
+                 :: "r"(smem_addr(smem_dst)), "l"(tensor_map), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(z), "r"(w), "l"(policy) : "memory");
+}
+__device__ __forceinline__ void prefetch_tensor_map(const void* tensor_map) {
+    asm volatile("prefetch.tensormap [%0];" :: "l"(tensor_map) : "memory");
+}
+
+// Order generic-proxy shared-memory writes before later async-proxy accesses
+// (needed before a TMA store or an MMA that reads what threads just wrote).
+__device__ __forceinline__ void fence_proxy_async_smem() {
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// ---- ring of stages ---------------------------------------------------------------------
+// Producer / consumer bookkeeping for an N-stage ring: stage index and the
+// parity of the phase to wait for (the reference's AsyncTile2D ping/pong,
+// tensor_prefetch.hpp:151-196, generalised to N stages).
+template <int STAGES>
+struct Ring {
+    int stage = 0;
+    uint32_t phase = 0;
+    __device__ __forceinline__ void advance() {
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+    }
+};
+
+} // namespace dme

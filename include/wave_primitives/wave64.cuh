@@ -149,6 +149,21 @@ __device__ __forceinline__ T segment_reduce(const T (&v)[VEC], Op op) {
 }
 
 // ---------------------------------------------------------------------------
+// lane_group_reduce<LANES>: xor-butterfly reduction over aligned groups of
+// LANES lanes (2, 4, 8, 16 or 32); every lane of a group gets the result.
+// The attention kernels use it for online-softmax row max / row sum where a
+// score row is spread over a lane group (4 lanes in the MMA accumulator
+// layout, 8 lanes in the vector decode kernel).
+// ---------------------------------------------------------------------------
+template <int LANES, typename T, typename Op>
+__device__ __forceinline__ T lane_group_reduce(T v, Op op) {
+    static_assert(LANES >= 1 && LANES <= 32 && (LANES & (LANES - 1)) == 0, "power of two");
+    #pragma unroll
+    for (int m = 1; m < LANES; m <<= 1) v = op(v, detail::shfl_xor(v, m));
+    return v;
+}
+
+// ---------------------------------------------------------------------------
 // Kogge-Stone inclusive scan over rows of ROW consecutive elements, VEC per
 // lane.  Step with offset o: x[i] = op(x[i], i-o inside the row ? x[i-o] : id).
 // This is the association of the reference's row_shr cascade (ROW = 16,
