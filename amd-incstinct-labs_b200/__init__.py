@@ -37,7 +37,15 @@ SYMBOLS = {
     "b200p_attn_decode_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "b200p_attn_merge_lse": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
     "b200p_attn_workspace_status": (_i, [_vp, _vp]),
+    "b200p_attn_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "b200p_attn_prefill_debug": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
+    "b200p_device_status": (_i, [_i]),
 }
+
+
+class PrefillCfg(C.Structure):
+    """struct b200p_prefill_cfg == cdna3::attn::PrefillCfg."""
+    _fields_ = [("D", _i), ("seqQ", _i), ("seqK", _i), ("nQHeads", _i), ("nKVHeads", _i), ("batch", _i), ("causal", _i)]
 
 
 class DecodeArgs(C.Structure):
@@ -222,3 +230,29 @@ def merge_lse(o_parts, lse_parts, dtype, out=None):
 def workspace_status(workspace) -> int:
     """0, or B200P_E_TIMEOUT if a kernel using this workspace abandoned a bounded wait (synchronises)."""
     return int(lib().b200p_attn_workspace_status(workspace.data_ptr(), _stream(workspace)))
+
+
+# ---- prefill attention (cdna3::attn::prefill) ----------------------------------------------
+def prefill(Q, K, V, causal: bool = False, out=None, raw_scores=None):
+    """Q [batch, nQH, seqQ, D], K/V [batch, nKVH, seqK, D] (fp16 or bf16) -> O like Q."""
+    import torch
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V")):
+        _dev(t, n)
+    batch, nQH, seqQ, D = Q.shape
+    _, nKVH, seqK, _ = K.shape
+    cfg = PrefillCfg(D, seqQ, seqK, nQH, nKVH, batch, int(causal))
+    if out is None:
+        out = torch.empty_like(Q)
+    if raw_scores is None:
+        st = lib().b200p_attn_prefill(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), C.byref(cfg),
+                                      _dtype_code(Q), _stream(Q))
+    else:
+        st = lib().b200p_attn_prefill_debug(Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), C.byref(cfg),
+                                            _dtype_code(Q), raw_scores.data_ptr(), _stream(Q))
+    _check(st, "attn_prefill")
+    return out
+
+
+def device_status(clear: bool = True) -> int:
+    """0, or B200P_E_TIMEOUT if a kernel abandoned a bounded wait (synchronises the device)."""
+    return int(lib().b200p_device_status(int(clear)))

@@ -15,4 +15,11 @@ __device__ __forceinline__ float to_float(float f)         { return f; }
 __device__ __forceinline__ float to_float(__half f)        { return __half2float(f); }
 __device__ __forceinline__ float to_float(__nv_bfloat16 f) { return __bfloat162float(f); }
 
+// 2^x on the SFU; -inf gives +0.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 } // namespace b200p

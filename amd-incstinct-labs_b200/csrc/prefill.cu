@@ -1,0 +1,387 @@
+// ---------------------------------------------------------------------------
+// prefill.cu -- FA2 prefill attention on the 5th-generation tensor cores.
+//
+// Stands in for fa_multiwave_kernel<D,W> behind cdna3::attn::prefill
+// (cdna3-prims/include/cdna3/detail/fa_prefill_kernel.hpp:43-177,
+//  cdna3-prims/include/cdna3/attention.hpp:86-109) and for the MFMA step of the
+// reference's build order (research/flash-attention-mi300x/fa_mfma2.hip:63-217).
+// Same semantics: GQA (kvhead = qhead / group), causal mask "key > query is
+// masked", KV tiles past the diagonal skipped, scale 1/sqrt(D), fp32 softmax,
+// 16-bit output, O / l with l > 0 guarded.
+//
+// The reference keeps S, P and O in LDS, one 16-row block per wave, and rescales
+// O serially on lane 0.  Here a CTA owns 256 query rows of one (batch, head) as
+// two 128-row tiles and is warp-specialised:
+//   warp 9        TMA producer: Q once, then K_j / V_j tiles ([128][D], 64-element
+//                 boxes, 128-byte swizzle) into two mbarrier rings;
+//   warp 8        MMA issuer (one thread): S_t = Q_t.K_j^T and O_t += P_t.V_j as
+//                 tcgen05.mma with the accumulators in tensor memory; P_t is read
+//                 straight from tensor memory (it overwrites S_t as 16-bit pairs);
+//                 issue order PV_j^0, QK_{j+1}^0, PV_j^1, QK_{j+1}^1 so that one
+//                 tile's softmax overlaps the other tile's matrix work;
+//   warps 0-3/4-7 softmax for tile 0 / 1: one query row per thread (tcgen05.ld
+//                 32x32b gives a thread its whole row, so row max and row sum need
+//                 no cross-lane step at all), exp2 with the scale folded in, lazy
+//                 rescaling of O (only when the running max grew by more than 2^8),
+//                 final O / l and the store.
+// TMEM columns: S_0 [0,128) S_1 [128,256) O_0 [256,256+D) O_1 [384,384+D).
+// Compute-bound on the bf16 tensor pipe; K/V are re-read from L2 by the CTAs of
+// the same (batch, kv head), which are adjacent in the grid.
+//
+// Every mbarrier wait is bounded; a wait that gives up raises the library's
+// device status word and the CTA drains and frees its tensor memory.
+// ---------------------------------------------------------------------------
+#include "common.cuh"
+#include "attn_common.cuh"
+#include "dme/dme_tma.cuh"
+#include "tcgen05.cuh"
+#include "tensor_map.cuh"
+#include "mma_sync.cuh"
+
+namespace b200p {
+
+__device__ int g_device_status = 0;      // raised by kernels whose bounded wait gave up
+
+namespace {
+
+constexpr int kBM = 128;                 // query rows per tile
+constexpr int kBN = 128;                 // keys per tile
+constexpr int kPrefillThreads = 320;     // 2 softmax warpgroups + MMA warp + TMA warp
+constexpr int kMmaWarp = 8, kTmaWarp = 9;
+constexpr float kLazyRescale = 8.0f;     // log2 units
+
+template <int D> struct PrefillShape {
+    static constexpr int SUB = D / 64;                         // 64-element boxes per row
+    static constexpr int SUB_BYTES = kBM * 128;                // [128 rows][128 B]
+    static constexpr int TILE_BYTES = SUB * SUB_BYTES;         // one Q / K / V tile
+    static constexpr int KSTAGES = (D == 128) ? 2 : 4;
+    static constexpr int VSTAGES = (D == 128) ? 2 : 4;
+    static constexpr int OFF_Q = 0;
+    static constexpr int OFF_K = 2 * TILE_BYTES;
+    static constexpr int OFF_V = OFF_K + KSTAGES * TILE_BYTES;
+    static constexpr int OFF_BAR = OFF_V + VSTAGES * TILE_BYTES;
+    static constexpr int SMEM_BYTES = OFF_BAR + 1024;
+};
+
+struct PrefillParams {
+    void* O;
+    float* debug_s;            // optional: raw S of tile (0,0) of CTA (0,0,0), [128][128] fp32
+    int seqQ, seqK, nQH, nKVH, group, batch, causal;
+    float scale_log2;
+};
+
+template <typename T> struct Fmt;
+template <> struct Fmt<__half>        { static constexpr int id = 0; };
+template <> struct Fmt<__nv_bfloat16> { static constexpr int id = 1; };
+
+template <typename T, int D>
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ,
+                  const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
+    using Sh = PrefillShape<D>;
+    constexpr int KST = Sh::KSTAGES, VST = Sh::VSTAGES;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + Sh::OFF_BAR);
+    uint64_t* q_full  = bars;                 // [1]
+    uint64_t* k_full  = bars + 1;             // [KST]
+    uint64_t* k_empty = k_full + KST;
+    uint64_t* v_full  = k_empty + KST;        // [VST]
+    uint64_t* v_empty = v_full + VST;
+    uint64_t* s_full  = v_empty + VST;        // [2]
+    uint64_t* p_full  = s_full + 2;           // [2]
+    uint64_t* o_done  = p_full + 2;           // [2]
+    __shared__ uint32_t s_tmem_base;
+    __shared__ int s_failed;
+
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int nqb = (p.seqQ + 2 * kBM - 1) / (2 * kBM);
+    const int qb = nqb - 1 - int(blockIdx.x);                  // heaviest (latest) query blocks first
+    const int head = blockIdx.y, b = blockIdx.z;
+    const int kvh = head / p.group;
+    const int ntk = (p.seqK + kBN - 1) / kBN;
+    int q0[2], n[2];
+    #pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        q0[t] = qb * 2 * kBM + t * kBM;
+        if (q0[t] >= p.seqQ) n[t] = 0;
+        else if (p.causal) n[t] = min(ntk, (q0[t] + kBM - 1) / kBN + 1);
+        else n[t] = ntk;
+    }
+    const int nmax = max(n[0], n[1]);
+
+    if (threadIdx.x == 0) {
+        s_failed = 0;
+        dme::mbar_init(q_full, 1);
+        for (int s = 0; s < KST; ++s) { dme::mbar_init(&k_full[s], 1); dme::mbar_init(&k_empty[s], 1); }
+        for (int s = 0; s < VST; ++s) { dme::mbar_init(&v_full[s], 1); dme::mbar_init(&v_empty[s], 1); }
+        for (int t = 0; t < 2; ++t) { dme::mbar_init(&s_full[t], 1); dme::mbar_init(&p_full[t], kBM); dme::mbar_init(&o_done[t], 1); }
+        dme::mbar_init_fence();
+    }
+    if (warp == kMmaWarp) { tc::tmem_alloc(&s_tmem_base, 512); tc::tmem_relinquish(); }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    const uint32_t tmem = s_tmem_base;
+    const uint32_t sm_q = dme::smem_addr(smem + Sh::OFF_Q), sm_k = dme::smem_addr(smem + Sh::OFF_K), sm_v = dme::smem_addr(smem + Sh::OFF_V);
+
+    if (warp == kTmaWarp) {
+        // ---------------------------------- TMA producer ----------------------------------
+        if (lane == 0) {
+            dme::prefetch_tensor_map(&mapQ); dme::prefetch_tensor_map(&mapK); dme::prefetch_tensor_map(&mapV);
+            dme::mbar_arrive_expect_tx(q_full, uint32_t((n[0] > 0) + (n[1] > 0)) * Sh::TILE_BYTES);
+            for (int t = 0; t < 2; ++t) if (n[t] > 0)
+                for (int sb = 0; sb < Sh::SUB; ++sb)
+                    dme::copy_tile_4d(smem + Sh::OFF_Q + t * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapQ, sb * 64, q0[t], head, b, q_full);
+            dme::Ring<KST> kr; dme::Ring<VST> vr;
+            for (int j = 0; j < nmax; ++j) {
+                if (j >= KST && !dme::wait(&k_empty[kr.stage], kr.phase ^ 1u)) { atomicExch(&s_failed, 1); break; }
+                dme::mbar_arrive_expect_tx(&k_full[kr.stage], Sh::TILE_BYTES);
+                for (int sb = 0; sb < Sh::SUB; ++sb)
+                    dme::copy_tile_4d(smem + Sh::OFF_K + kr.stage * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapK, sb * 64, j * kBN, kvh, b, &k_full[kr.stage]);
+                kr.advance();
+                if (j >= VST && !dme::wait(&v_empty[vr.stage], vr.phase ^ 1u)) { atomicExch(&s_failed, 1); break; }
+                dme::mbar_arrive_expect_tx(&v_full[vr.stage], Sh::TILE_BYTES);
+                for (int sb = 0; sb < Sh::SUB; ++sb)
+                    dme::copy_tile_4d(smem + Sh::OFF_V + vr.stage * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapV, sb * 64, j * kBN, kvh, b, &v_full[vr.stage]);
+                vr.advance();
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ---------------------------------- MMA issuer ------------------------------------
+        if (lane == 0) {
+            constexpr uint32_t idesc_qk = tc::instr_desc_f16(kBM, kBN, Fmt<T>::id, 0, 0);
+            constexpr uint32_t idesc_pv = tc::instr_desc_f16(kBM, D, Fmt<T>::id, 0, 1);
+            auto issue_qk = [&](int t, int kstage) {
+                #pragma unroll
+                for (int ks = 0; ks < D / 16; ++ks) {
+                    const uint32_t off = uint32_t(ks / 4) * Sh::SUB_BYTES + uint32_t(ks % 4) * 32u;
+                    tc::mma_ss(tmem + t * kBN,
+                               tc::smem_desc_sw128(sm_q + t * Sh::TILE_BYTES + off, 16, 1024),
+                               tc::smem_desc_sw128(sm_k + kstage * Sh::TILE_BYTES + off, 16, 1024),
+                               idesc_qk, ks > 0);
+                }
+            };
+            auto issue_pv = [&](int t, int vstage, bool first) {
+                #pragma unroll
+                for (int kk = 0; kk < kBN / 16; ++kk)
+                    tc::mma_ts(tmem + 256 + t * 128, tmem + t * kBN + kk * 8,
+                               tc::smem_desc_sw128(sm_v + vstage * Sh::TILE_BYTES + kk * 2048, Sh::SUB_BYTES, 1024),
+                               idesc_pv, !(first && kk == 0));
+            };
+            bool ok = dme::wait(q_full, 0);
+            dme::Ring<KST> kr; dme::Ring<VST> vr;
+            if (ok && nmax > 0) {
+                ok = dme::wait(&k_full[kr.stage], kr.phase);
+                tc::fence_after_sync();
+                if (ok) {
+                    for (int t = 0; t < 2; ++t) if (n[t] > 0) { issue_qk(t, kr.stage); tc::commit(&s_full[t]); }
+                    tc::commit(&k_empty[kr.stage]);
+                    kr.advance();
+                }
+            }
+            for (int j = 0; j < nmax && ok; ++j) {
+                ok = dme::wait(&v_full[vr.stage], vr.phase);
+                if (ok && j + 1 < nmax) ok = dme::wait(&k_full[kr.stage], kr.phase);
+                if (!ok) break;
+                for (int t = 0; t < 2 && ok; ++t) {
+                    if (j >= n[t]) continue;
+                    ok = dme::wait(&p_full[t], uint32_t(j & 1));
+                    if (!ok) break;
+                    tc::fence_after_sync();
+                    issue_pv(t, vr.stage, j == 0);
+                    if (j + 1 < n[t]) { issue_qk(t, kr.stage); tc::commit(&s_full[t]); }
+                    else tc::commit(&o_done[t]);
+                }
+                tc::commit(&v_empty[vr.stage]);
+                vr.advance();
+                if (j + 1 < nmax) { tc::commit(&k_empty[kr.stage]); kr.advance(); }
+            }
+            if (!ok) atomicExch(&s_failed, 1);
+        }
+    } else {
+        // ---------------------------------- softmax warpgroups ----------------------------
+        const int t = warp / 4;                               // query tile of this warpgroup
+        const int r = threadIdx.x % kBM;                      // row inside the tile = TMEM lane
+        const int row = q0[t] + r;
+        const uint32_t lane_base = uint32_t(32 * (warp % 4)) << 16;
+        const uint32_t tS = tmem + lane_base + uint32_t(t * kBN);
+        const uint32_t tO = tmem + lane_base + 256u + uint32_t(t * 128);
+        float m_used = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n[t]; ++j) {
+            if (!dme::wait(&s_full[t], uint32_t(j & 1))) { ok = false; break; }
+            tc::fence_after_sync();
+            const bool need_mask = (p.causal && j * kBN + kBN - 1 > q0[t]) || (j * kBN + kBN > p.seqK);
+            const int col_limit = min(p.causal ? row : 0x7fffffff, p.seqK - 1) - j * kBN;   // columns <= col_limit are live
+            // ---- pass 1: row max -------------------------------------------------------
+            float mx = -INFINITY;
+            #pragma unroll
+            for (int c = 0; c < kBN / 32; ++c) {
+                uint32_t v[32];
+                tc::ld_32x32b_x32(tS + c * 32, v);
+                tc::wait_ld();
+                if (p.debug_s && j == 0 && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) p.debug_s[r * kBN + c * 32 + i] = __uint_as_float(v[i]);
+                }
+                #pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    float s = __uint_as_float(v[i]);
+                    if (need_mask && c * 32 + i > col_limit) s = -INFINITY;
+                    mx = fmaxf(mx, s);
+                }
+            }
+            const float m_new = mx * p.scale_log2;
+            float alpha = 1.f;
+            if (m_new > m_used + kLazyRescale) { alpha = fast_exp2(m_used - m_new); m_used = m_new; }
+            // ---- rescale O when some row of this warp moved its max (never on the first tile) ----
+            if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
+                #pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t v[32];
+                    tc::ld_32x32b_x32(tO + c * 32, v);
+                    tc::wait_ld();
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
+                    tc::st_32x32b_x32(tO + c * 32, v);
+                }
+                tc::wait_st();
+            }
+            // ---- pass 2: P = exp2(S * scale - m), 16-bit pairs over the front of S ---------
+            float l_add = 0.f;
+            #pragma unroll
+            for (int c = 0; c < kBN / 32; ++c) {
+                uint32_t v[32];
+                tc::ld_32x32b_x32(tS + c * 32, v);
+                tc::wait_ld();
+                uint32_t pk[16];
+                #pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float s0 = __uint_as_float(v[2 * i]), s1 = __uint_as_float(v[2 * i + 1]);
+                    if (need_mask) {
+                        if (c * 32 + 2 * i > col_limit) s0 = -INFINITY;
+                        if (c * 32 + 2 * i + 1 > col_limit) s1 = -INFINITY;
+                    }
+                    const float p0 = fast_exp2(fmaf(s0, p.scale_log2, -m_used));
+                    const float p1 = fast_exp2(fmaf(s1, p.scale_log2, -m_used));
+                    l_add += p0 + p1;
+                    pk[i] = pack2<T>(p0, p1);
+                }
+                tc::st_32x32b_x16(tS + c * 16, pk);
+            }
+            tc::wait_st();
+            l = l * alpha + l_add;
+            tc::fence_before_sync();
+            dme::mbar_arrive(&p_full[t]);
+        }
+        // ---- epilogue: O / l -> 16-bit, one row per thread -------------------------------
+        if (ok && n[t] > 0) {
+            if (dme::wait(&o_done[t], 0)) {
+                tc::fence_after_sync();
+                const float inv = l > 0.f ? 1.f / l : 1.f;
+                T* orow = static_cast<T*>(p.O) + ((size_t(b) * p.nQH + head) * p.seqQ + row) * D;
+                #pragma unroll
+                for (int c = 0; c < D / 32; ++c) {
+                    uint32_t v[32];
+                    tc::ld_32x32b_x32(tO + c * 32, v);
+                    tc::wait_ld();
+                    if (row < p.seqQ) {
+                        #pragma unroll
+                        for (int q4 = 0; q4 < 4; ++q4) {
+                            uint4 w;
+                            w.x = pack2<T>(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv);
+                            w.y = pack2<T>(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv);
+                            w.z = pack2<T>(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv);
+                            w.w = pack2<T>(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv);
+                            *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = w;
+                        }
+                    }
+                }
+            } else ok = false;
+        }
+        if (!ok) atomicExch(&s_failed, 1);
+    }
+    tc::fence_before_sync();
+    __syncthreads();
+    tc::fence_after_sync();
+    if (warp == kMmaWarp) tc::tmem_dealloc(tmem, 512);
+    if (threadIdx.x == 0 && s_failed) atomicExch(&g_device_status, 1);
+}
+
+template <typename T, int D>
+int launch_prefill(const void* Q, const void* K, const void* V, void* O, const b200p_prefill_cfg* c, int dtype,
+                   float* debug_s, cudaStream_t st) {
+    using Sh = PrefillShape<D>;
+    const CUtensorMapDataType dt = dtype == B200P_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+    CUtensorMap mq, mk, mv;
+    const uint64_t qd[4] = {uint64_t(D), uint64_t(c->seqQ), uint64_t(c->nQHeads), uint64_t(c->batch)};
+    const uint64_t qs[3] = {uint64_t(D) * 2, uint64_t(c->seqQ) * D * 2, uint64_t(c->nQHeads) * c->seqQ * D * 2};
+    const uint64_t kd[4] = {uint64_t(D), uint64_t(c->seqK), uint64_t(c->nKVHeads), uint64_t(c->batch)};
+    const uint64_t ks[3] = {uint64_t(D) * 2, uint64_t(c->seqK) * D * 2, uint64_t(c->nKVHeads) * c->seqK * D * 2};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    cudaError_t e = make_tensor_map(&mq, dt, 4, Q, qd, qs, box, Swizzle::B128);
+    if (e == cudaSuccess) e = make_tensor_map(&mk, dt, 4, K, kd, ks, box, Swizzle::B128);
+    if (e == cudaSuccess) e = make_tensor_map(&mv, dt, 4, V, kd, ks, box, Swizzle::B128);
+    if (e != cudaSuccess) return int(e);
+
+    auto kern = prefill_tc_kernel<T, D>;
+    static bool attr_set[64] = {};
+    int dev = 0; cudaGetDevice(&dev);
+    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+        e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Sh::SMEM_BYTES);
+        if (e != cudaSuccess) return int(e);
+        attr_set[dev] = true;
+    }
+    PrefillParams p{};
+    p.O = O; p.debug_s = debug_s;
+    p.seqQ = c->seqQ; p.seqK = c->seqK; p.nQH = c->nQHeads; p.nKVH = c->nKVHeads; p.group = c->nQHeads / c->nKVHeads;
+    p.batch = c->batch; p.causal = c->causal;
+    p.scale_log2 = 1.4426950408889634f / sqrtf(float(D));
+    dim3 grid((c->seqQ + 2 * kBM - 1) / (2 * kBM), c->nQHeads, c->batch);
+    kern<<<grid, kPrefillThreads, Sh::SMEM_BYTES, st>>>(p, mq, mk, mv);
+    return launched();
+}
+
+} // namespace
+
+int prefill_dispatch(const void* Q, const void* K, const void* V, void* O, const b200p_prefill_cfg* c, int dtype,
+                     float* debug_s, cudaStream_t st) {
+    if (!c) return B200P_E_NULL;
+    if (dtype != B200P_F16 && dtype != B200P_BF16) return B200P_E_DTYPE;
+    if (c->D != 64 && c->D != 128) return B200P_E_DIM;                        // attention.hpp:105-107
+    if (c->nQHeads <= 0 || c->nKVHeads <= 0 || c->nQHeads % c->nKVHeads != 0) return B200P_E_DIM;
+    if (c->seqQ <= 0 || c->seqK <= 0 || c->batch <= 0) return B200P_E_LENGTH;
+    if (c->nQHeads > 65535 || c->batch > 65535) return B200P_E_RANGE;
+    if (!Q || !K || !V || !O) return B200P_E_NULL;
+    if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16)) return B200P_E_ALIGN;
+    if (sm_count() <= 0) return B200P_E_NO_DEVICE;
+    if (dtype == B200P_F16)
+        return c->D == 128 ? launch_prefill<__half, 128>(Q, K, V, O, c, dtype, debug_s, st)
+                           : launch_prefill<__half, 64>(Q, K, V, O, c, dtype, debug_s, st);
+    return c->D == 128 ? launch_prefill<__nv_bfloat16, 128>(Q, K, V, O, c, dtype, debug_s, st)
+                       : launch_prefill<__nv_bfloat16, 64>(Q, K, V, O, c, dtype, debug_s, st);
+}
+
+} // namespace b200p
+
+using namespace b200p;
+
+extern "C" int b200p_attn_prefill(const void* Q, const void* K, const void* V, void* O,
+                                  const b200p_prefill_cfg* cfg, int dtype, b200p_stream_t stream) {
+    return prefill_dispatch(Q, K, V, O, cfg, dtype, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200p_attn_prefill_debug(const void* Q, const void* K, const void* V, void* O,
+                                        const b200p_prefill_cfg* cfg, int dtype, float* raw_scores,
+                                        b200p_stream_t stream) {
+    return prefill_dispatch(Q, K, V, O, cfg, dtype, raw_scores, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200p_device_status(int clear) {
+    int h = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&h, g_device_status, sizeof(int));
+    if (e == cudaSuccess && clear && h != 0) { int z = 0; e = cudaMemcpyToSymbol(g_device_status, &z, sizeof(int)); }
+    if (e != cudaSuccess) return int(e);
+    return h == 0 ? B200P_OK : B200P_E_TIMEOUT;
+}

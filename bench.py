@@ -288,7 +288,76 @@ class DecodeGQA:
     cpu_sample_text = "8 of the 64 sequences at full KV length"
 
 
-WORKLOADS = {"segops": SegopsSweep, "decode": DecodeGQA}
+# --------------------------------------------------------------------------------------
+# workload: causal prefill (BASELINE config 3)
+# --------------------------------------------------------------------------------------
+class PrefillCausal:
+    name = "prefill"
+    metric = "FA2 causal prefill attention throughput"
+    unit = "TFLOP/s"
+    dtype = "bf16 (fp32 softmax and accumulation)"
+    B, H, S, D = 8, 32, 4096, 128
+    bound = "tensor"
+
+    def __init__(self, n=None):
+        if n:
+            self.S = n
+        # the reference's FLOP convention for causal attention: 2 GEMMs x 2 flops, half the square
+        # (research/flash-attention-mi300x/fa_robust.hip:266-268)
+        self.flops_per_step = 2.0 * 2.0 * self.B * self.H * self.S * self.S * self.D * 0.5
+        self.bytes_per_step = self.flops_per_step        # "units" the generic code divides by time
+        self.cases = [("prefill_tc_kernel", None, None, None, self.flops_per_step)]
+
+    def config(self, world):
+        return {"workload": "FA2 causal prefill (BASELINE config 3)", "batch_per_gpu": self.B, "heads": self.H, "seq_len": self.S,
+                "head_dim": self.D, "causal": True, "sharding": f"(batch, head) x{world}, no collective",
+                "flops": "2*2*B*H*S*S*D/2 (the reference's convention)",
+                "l2": "Q,K,V,O (4 x 268 MB) larger than L2", "inputs": "Q, K, V ~ N(0,1)*0.5 rounded to bf16, seeded"}
+
+    def setup(self, torch, pkg, device, rank):
+        self.torch, self.pkg = torch, pkg
+        g = torch.Generator(device=device); g.manual_seed(0xB203 + 1000 * rank)
+        shape = (self.B, self.H, self.S, self.D)
+        self.Q = (torch.randn(shape, device=device, generator=g) * 0.5).bfloat16()
+        self.K = (torch.randn(shape, device=device, generator=g) * 0.5).bfloat16()
+        self.V = (torch.randn(shape, device=device, generator=g) * 0.5).bfloat16()
+        self.O = torch.empty_like(self.Q)
+        self.host = [t.cpu().pin_memory() for t in (self.Q, self.K, self.V)]
+        self.O_host = torch.empty(shape, dtype=torch.bfloat16).pin_memory()
+        torch.cuda.synchronize()
+
+    def step(self, events=None):
+        self.pkg.prefill(self.Q, self.K, self.V, causal=True, out=self.O)
+        if events is not None:
+            e = self.torch.cuda.Event(enable_timing=True); e.record(); events.append(e)
+
+    def step_e2e(self):
+        for d, h in zip((self.Q, self.K, self.V), self.host):
+            d.copy_(h, non_blocking=True)
+        self.step()
+        self.O_host.copy_(self.O, non_blocking=True)
+
+    def e2e_bytes(self):
+        return 3 * self.Q.numel() * 2, self.O.numel() * 2
+
+    def cpu_run(self, orc, n, threads, reps=1):
+        """n = (batch, head) units at full sequence length."""
+        import numpy as np
+        rng = np.random.default_rng(0xB203)
+        q = (rng.standard_normal((n, self.S, self.D), dtype=np.float32) * 0.5)
+        k = (rng.standard_normal((n, self.S, self.D), dtype=np.float32) * 0.5)
+        v = (rng.standard_normal((n, self.S, self.D), dtype=np.float32) * 0.5)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            orc.cpu_prefill(q, k, v, self.D, self.S, self.S, n, n, 1, 1, threads=threads)
+        dt = (time.perf_counter() - t0) / reps
+        return self.flops_per_step * (n / (self.B * self.H)) / dt / 1e12, dt
+
+    cpu_sample = 16
+    cpu_sample_text = "16 of the 256 (batch, head) units at full sequence length"
+
+
+WORKLOADS = {"segops": SegopsSweep, "decode": DecodeGQA, "prefill": PrefillCausal}
 
 
 # --------------------------------------------------------------------------------------
@@ -383,7 +452,10 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms = float(t.item())
     ms_per_step = total_ms / args.steps
-    value = world * wl.bytes_per_step / (ms_per_step * 1e-3) / 1e9
+    tensor_bound = getattr(wl, "bound", "hbm") == "tensor"
+    unit_scale = 1e12 if tensor_bound else 1e9
+    peak = peaks["bf16_tflops"] if tensor_bound else peaks["hbm_gbs"]
+    value = world * wl.bytes_per_step / (ms_per_step * 1e-3) / unit_scale
 
     # per-kernel durations (average over the timed steps)
     ncase = len(wl.cases)
@@ -394,13 +466,14 @@ def main():
     kernels = []
     for i, (label, fn, kind, op, nbytes) in enumerate(wl.cases):
         us = max(per[i] / args.steps * 1e3, 1e-3)
-        gbs = nbytes / (us * 1e-6) / 1e9
-        kernels.append({"kernel": label, "us": round(us, 2), "bytes": nbytes, "GB/s": round(gbs, 1),
-                        "frac": round(gbs / peaks["hbm_gbs"], 4)})
+        gbs = nbytes / (us * 1e-6) / unit_scale
+        kernels.append({"kernel": label, "us": round(us, 2), "flops" if tensor_bound else "bytes": nbytes,
+                        wl.unit: round(gbs, 1), "frac": round(gbs / peak, 4)})
     dom = max(range(ncase), key=lambda i: per[i])
-    roofline = {"bound": "hbm", "kernel": kernels[dom]["kernel"], "achieved": kernels[dom]["GB/s"],
-                "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": kernels[dom]["frac"],
-                "peak_source": f"{peaks['source']} copy bandwidth", "traffic": TRAFFIC.get(kernels[dom]["kernel"])}
+    roofline = {"bound": "tensor" if tensor_bound else "hbm", "kernel": kernels[dom]["kernel"], "achieved": kernels[dom][wl.unit],
+                "peak": peak, "unit": wl.unit, "frac": kernels[dom]["frac"],
+                "peak_source": f"{peaks['source']} " + ("cuBLAS bf16 burst" if tensor_bound else "copy bandwidth"),
+                "traffic": TRAFFIC.get(kernels[dom]["kernel"])}
 
     # ---- end to end: host buffers in, host results out, every step ----------------------
     e2e_steps = args.e2e_steps or max(3, min(args.steps, 10))
@@ -417,7 +490,7 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     e2e_ms = float(t.item()) / e2e_steps
     h2d, d2h = wl.e2e_bytes()
-    e2e = {"value": world * wl.bytes_per_step / (e2e_ms * 1e-3) / 1e9, "unit": wl.unit, "ms_per_step": e2e_ms,
+    e2e = {"value": world * wl.bytes_per_step / (e2e_ms * 1e-3) / unit_scale, "unit": wl.unit, "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps}
 
     # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------

@@ -157,6 +157,38 @@ int b200p_attn_merge_lse(const float* o_parts, const float* lse_parts, int parts
  * abandoned a bounded wait (B200P_E_TIMEOUT) or not (0). */
 int b200p_attn_workspace_status(const void* workspace, b200p_stream_t stream);
 
+/* cdna3::attn::PrefillCfg, field for field (attention.hpp:63-71). */
+typedef struct b200p_prefill_cfg {
+    int D;          /* head dimension: 64 or 128                         */
+    int seqQ;       /* query length (any; the reference needs a multiple of 16*W) */
+    int seqK;       /* key/value length                                  */
+    int nQHeads;
+    int nKVHeads;   /* nQHeads % nKVHeads == 0                           */
+    int batch;
+    int causal;     /* 1: key k is masked for query q iff k > q          */
+} b200p_prefill_cfg;
+
+/* Stands in for cdna3::attn::prefill (attention.hpp:86-109) and its kernel
+ * fa_multiwave_kernel<D,W> (cdna3-prims/include/cdna3/detail/
+ * fa_prefill_kernel.hpp:43-177).  Q,O [batch, nQH, seqQ, D]; K,V
+ * [batch, nKVH, seqK, D]; dtype B200P_F16 or B200P_BF16.  Unsupported D returns
+ * B200P_E_DIM before any launch, as the reference returns hipErrorInvalidValue. */
+int b200p_attn_prefill(const void* Q, const void* K, const void* V, void* O,
+                       const b200p_prefill_cfg* cfg, int dtype, b200p_stream_t stream);
+
+/* The same launch, additionally writing the raw (unscaled) fp32 score tile
+ * S = Q.K^T of the LAST 256-row query block's first 128 rows against keys
+ * 0..127 of (batch 0, head 0) to raw_scores[128][128]: the known-answer probe
+ * of the tensor-core operand layouts (the role of the reference's
+ * research/flash-attention-mi300x/tests/probe_mfma_mapping.hip). */
+int b200p_attn_prefill_debug(const void* Q, const void* K, const void* V, void* O,
+                             const b200p_prefill_cfg* cfg, int dtype, float* raw_scores,
+                             b200p_stream_t stream);
+
+/* Synchronises the device and reports whether any kernel of this library
+ * abandoned a bounded wait since the last clear (B200P_E_TIMEOUT) or not (0). */
+int b200p_device_status(int clear);
+
 #ifdef __cplusplus
 }
 #endif

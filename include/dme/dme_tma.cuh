@@ -11,7 +11,7 @@
 // engine (cp.async.bulk) and completion is signalled through an mbarrier that
 // the consumers poll, so any number of stages can be in flight.
 //
-// Every wait is BOUNDED: wait() returns false after kSpinLimit polls instead of
+// Every wait is BOUNDED: wait() returns false after kWaitLimitNs instead of
 // spinning for ever, so a lost copy turns into an error status, not a hang.
 //
 // Alignment: source, destination and byte count of a bulk copy must be
@@ -23,7 +23,7 @@
 
 namespace dme {
 
-constexpr uint32_t kSpinLimit = 1u << 24;   // polls; try_wait itself blocks for a while per poll
+constexpr uint64_t kWaitLimitNs = 2000000000ull;   // a wait gives up after ~2 s of wall time
 
 __device__ __forceinline__ uint32_t smem_addr(const void* p) {
     return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -54,11 +54,22 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// Bounded wait for the phase with the given parity.  false = gave up.
+__device__ __forceinline__ uint64_t global_timer_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Bounded wait for the phase with the given parity.  false = gave up (after
+// kWaitLimitNs; the clock is read once per 256 polls).
 __device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity) {
-    for (uint32_t i = 0; i < kSpinLimit; ++i)
-        if (mbar_try_wait(bar, parity)) return true;
-    return false;
+    if (mbar_try_wait(bar, parity)) return true;
+    const uint64_t t0 = global_timer_ns();
+    for (;;) {
+        #pragma unroll 1
+        for (int i = 0; i < 256; ++i)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+    }
 }
 
 // ---- L2 policy for data that is read exactly once -------------------------------------
