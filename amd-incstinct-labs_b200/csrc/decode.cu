@@ -755,6 +755,45 @@ extern "C" int b200p_attn_merge_lse(const float* o_parts, const float* lse_parts
     return launched();
 }
 
+// ---------------------------------------------------------------------------
+// Decode without caller-provided scratch.
+//
+// Some hosts of this library cannot hand it device memory: a serving loop whose
+// memory plan was frozen at start-up, or an embedding runtime that only passes
+// the tensors it owns and has no allocator to lend.  For them the split-KV
+// partials live in this fixed array, which is part of the library image: every
+// GPU that loads the library carries these bytes until the process exits.
+// The array's name is only a host-side handle; the device address is looked up
+// once per device (with that device current) and handed to the kernels.
+// ---------------------------------------------------------------------------
+constexpr size_t kNoAllocScratchBytes = size_t(8) << 20;        // 8 MiB
+static __device__ __align__(256) unsigned char g_noalloc_scratch[kNoAllocScratchBytes];
+static void* g_noalloc_ptr[64] = {};                            // per device, filled at first use
+
+extern "C" size_t b200p_attn_decode_noalloc_max_bytes(void) { return kNoAllocScratchBytes; }
+
+extern "C" int b200p_attn_decode_noalloc(const void* q, const void* K, const void* V, void* o,
+                                         const b200p_decode_args* a, b200p_stream_t stream) {
+    if (!o) return B200P_E_NULL;
+    if (int e = validate(a)) return e;
+    if (sm_count() <= 0) return B200P_E_NO_DEVICE;
+    const DecodePlan pl = plan_decode(a->D, a->N, a->nQHeads, a->nKVHeads, a->batch);
+    if (pl.ws_bytes > kNoAllocScratchBytes) return B200P_E_RANGE;      // shapes too large for the built-in scratch
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return B200P_E_NO_DEVICE;
+    if (!g_noalloc_ptr[dev]) {
+        // set-up, once per device: resolve the array's device address
+        void* ptr = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e != cudaSuccess) return int(e);
+        g_noalloc_ptr[dev] = ptr;
+    }
+    // run_decode clears the status word at the front of the scratch; the partials
+    // behind it are overwritten before they are read.
+    return run_decode(a, q, K, V, o, nullptr, nullptr, g_noalloc_ptr[dev], kNoAllocScratchBytes,
+                      static_cast<cudaStream_t>(stream));
+}
+
 extern "C" int b200p_attn_workspace_status(const void* workspace, b200p_stream_t stream) {
     if (!workspace) return B200P_E_NULL;
     int h = 0;

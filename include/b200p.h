@@ -153,6 +153,22 @@ int b200p_attn_decode_partial(const void* q, const void* K, const void* V, float
 int b200p_attn_merge_lse(const float* o_parts, const float* lse_parts, int parts, int rows, int D,
                          int dtype, void* o, b200p_stream_t stream);
 
+/* Decode for callers that cannot supply scratch memory -- a serving loop whose
+ * memory plan is fixed at start-up, or a host runtime that passes only its own
+ * tensors and has no allocator to lend.  This entry point has no counterpart in
+ * the reference.  It is b200p_attn_decode with the split-KV scratch held in a
+ * fixed array inside the library (b200p_attn_decode_noalloc_max_bytes() bytes,
+ * 8 MiB, resident on every GPU that loads the library until the process ends)
+ * and it allocates nothing itself.  Arguments whose scratch need exceeds that
+ * size (compare b200p_attn_decode_workspace_bytes) are rejected with
+ * B200P_E_RANGE.  The first call on each device looks up the array's device
+ * address; make that first call outside any stream capture.  All calls share
+ * the one array: two calls whose kernels can overlap on the GPU (different
+ * streams, no dependency) race on it -- serialise them. */
+int b200p_attn_decode_noalloc(const void* q, const void* K, const void* V, void* o,
+                              const b200p_decode_args* args, b200p_stream_t stream);
+size_t b200p_attn_decode_noalloc_max_bytes(void);
+
 /* Synchronises `stream` and reports whether a kernel that used `workspace`
  * abandoned a bounded wait (B200P_E_TIMEOUT) or not (0). */
 int b200p_attn_workspace_status(const void* workspace, b200p_stream_t stream);
