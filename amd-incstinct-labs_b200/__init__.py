@@ -42,6 +42,7 @@ SYMBOLS = {
     "b200p_attn_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp]),
     "b200p_attn_prefill_debug": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
     "b200p_device_status": (_i, [_i]),
+    "b200p_fa_step": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.c_float, _vp]),
 }
 
 
@@ -275,3 +276,21 @@ def prefill(Q, K, V, causal: bool = False, out=None, raw_scores=None):
 def device_status(clear: bool = True) -> int:
     """0, or B200P_E_TIMEOUT if a kernel abandoned a bounded wait (synchronises the device)."""
     return int(lib().b200p_device_status(int(clear)))
+
+
+FA_STEPS = {"naive": 0, "dpp": 1, "dme": 2, "mfma2": 3}
+
+
+def fa_step(step: str, Q, K, V, scale: float = 0.0, out=None):
+    """One of the reference's FA2 build-order steps (fa_naive / fa_dpp / fa_dme / fa_mfma2).
+    Q,K,V [batch, heads, seq, D] in fp16, bf16 or (steps naive/dpp/dme) fp32."""
+    import torch
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V")):
+        _dev(t, n)
+    batch, heads, sq, D = Q.shape
+    sk = K.shape[2]
+    if out is None:
+        out = torch.empty_like(Q)
+    _check(lib().b200p_fa_step(FA_STEPS[step], _dtype_code(Q), Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(),
+                               batch, heads, sq, sk, D, float(scale), _stream(Q)), "fa_step")
+    return out

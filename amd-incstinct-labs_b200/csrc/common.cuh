@@ -25,6 +25,10 @@ enum Knob {
     KNOB_COUNT
 };
 
+// Device address of the library's status word on the current device (raised by
+// kernels whose bounded wait gave up), or nullptr without a device.
+int* device_status_ptr();
+
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 
 // Record a launch and translate the launch status.

@@ -42,6 +42,18 @@ namespace b200p {
 
 __device__ int g_device_status = 0;      // raised by kernels whose bounded wait gave up
 
+int* device_status_ptr() {
+    static int* ptrs[64] = {};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return nullptr; }
+    if (!ptrs[dev]) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        ptrs[dev] = static_cast<int*>(p);
+    }
+    return ptrs[dev];
+}
+
 namespace {
 
 constexpr int kBM = 128;                 // query rows per tile

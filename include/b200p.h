@@ -201,6 +201,21 @@ int b200p_attn_prefill_debug(const void* Q, const void* K, const void* V, void* 
                              const b200p_prefill_cfg* cfg, int dtype, float* raw_scores,
                              b200p_stream_t stream);
 
+/* The reference's FA2 build-order steps at their own tiling (Br = 16 query rows
+ * per block, Bc = 64 keys per tile, one warp per query row), MHA, non-causal:
+ *   step 0  fa_naive  research/flash-attention-mi300x/fa_naive.hip:72-212
+ *   step 1  fa_dpp    research/flash-attention-mi300x/fa_dpp.hip:52-167
+ *   step 2  fa_dme    research/flash-attention-mi300x/fa_dme.hip:74-221
+ *   step 3  fa_mfma2  research/flash-attention-mi300x/fa_mfma2.hip:63-217
+ *           (the tensor-core kernel of b200p_attn_prefill; 16-bit types only)
+ * Q,K,V,O [batch, heads, seq, D]; dtype B200P_F16 (the reference's), B200P_BF16
+ * or, for steps 0-2, B200P_F32 -- the fp32-I/O kernels whose launch takes
+ * (seq_len, n_heads, scale): research/flash-attention-mi300x/kernels/
+ * fa_naive.hip:118-278, kernels/fa_dpp.hip:167-313.  scale = 0 means 1/sqrt(D).
+ * seq_q % 16 == 0 and seq_k % 64 == 0 for steps 0-2 (the reference's tiling). */
+int b200p_fa_step(int step, int dtype, const void* Q, const void* K, const void* V, void* O,
+                  int batch, int heads, int seq_q, int seq_k, int D, float scale, b200p_stream_t stream);
+
 /* Synchronises the device and reports whether any kernel of this library
  * abandoned a bounded wait since the last clear (B200P_E_TIMEOUT) or not (0). */
 int b200p_device_status(int clear);

@@ -1,0 +1,21 @@
+// Host-only translation unit: the reference-shaped C++ API compiles with a plain C++
+// compiler and links against libb200p.so.  Mirrors the call shapes of
+// cdna3-prims/tests/validate_attention_api.hip:95,128 and
+// cdna3-prims/tests/validate_decode_dme.hip:109-117 (no device work is done here).
+#include <cstdio>
+#include "cdna3/attention.hpp"
+
+int main() {
+    cdna3::attn::PrefillCfg pcfg{128, 256, 256, 4, 2, 1, 1};
+    cdna3::attn::DecodeCfg dcfg{128, 512, 32, 8};
+    cdna3::attn::DecodeDmeCfg mcfg{64, 256, 14, 2, 1024};
+    // argument errors are reported before any launch, with or without a GPU
+    int e1 = cdna3::attn::prefill<__half>(nullptr, nullptr, nullptr, nullptr, pcfg);
+    cdna3::attn::PrefillCfg bad = pcfg; bad.D = 96;
+    int e2 = cdna3::attn::prefill<__half>(nullptr, nullptr, nullptr, nullptr, bad);
+    int e3 = cdna3::attn::decode<__half>(nullptr, nullptr, nullptr, nullptr, dcfg, nullptr, 0);
+    int e4 = cdna3::attn::decode_dme<__nv_bfloat16>(nullptr, nullptr, nullptr, nullptr, mcfg);
+    size_t ws = cdna3::attn::decode_workspace_bytes(dcfg);
+    std::printf("%d %d %d %d %zu %s\n", e1, e2, e3, e4, ws, b200p_version());
+    return (e1 == B200P_E_NULL && e2 == B200P_E_DIM && e3 < 0 && e4 < 0 && ws > 0) ? 0 : 1;
+}

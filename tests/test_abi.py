@@ -48,3 +48,16 @@ def test_no_cpu_fallback(b200p):
     x = torch.zeros(64)
     with pytest.raises(ValueError):
         b200p.segreduce(x)
+
+
+def test_cpp_api_header_compiles_and_links(b200p, tmp_path):
+    """include/cdna3/attention.hpp (the reference-shaped C++ API) builds with g++ alone and
+    links against the C-ABI library; argument errors come back without touching a GPU."""
+    import subprocess
+    exe = tmp_path / "api_compile"
+    lib_dir = os.path.dirname(b200p.LIB_PATH)
+    subprocess.run(["g++", "-std=c++17", "-I" + os.path.join(ROOT, "include"), "-I/usr/local/cuda/include",
+                    os.path.join(ROOT, "tests", "cpp", "api_compile.cpp"), "-L" + lib_dir, "-lb200p",
+                    "-Wl,-rpath," + lib_dir, "-o", str(exe)], check=True)
+    r = subprocess.run([str(exe)], capture_output=True, text=True)
+    assert r.returncode == 0, r.stdout + r.stderr
