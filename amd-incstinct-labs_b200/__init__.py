@@ -35,7 +35,7 @@ SYMBOLS = {
     "b200p_attn_decode_workspace_bytes": (_sz, [_vp]),
     "b200p_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "b200p_attn_decode_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
-    "b200p_attn_merge_lse": (_i, [_vp, _vp, _i, _i, _i, _i, _vp, _vp]),
+    "b200p_attn_merge_lse": (_i, [_vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]),
     "b200p_attn_workspace_status": (_i, [_vp, _vp]),
     "b200p_attn_decode_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "b200p_attn_decode_noalloc_max_bytes": (_sz, []),
@@ -242,8 +242,20 @@ def merge_lse(o_parts, lse_parts, dtype, out=None):
     rows = lse_parts[0].numel()
     if out is None:
         out = torch.empty(o_parts.shape[1:], dtype=dtype, device=o_parts.device)
-    _check(lib().b200p_attn_merge_lse(o_parts.data_ptr(), lse_parts.data_ptr(), parts, rows, D, _dtype_code(out),
+    _check(lib().b200p_attn_merge_lse(o_parts.data_ptr(), lse_parts.data_ptr(), parts, rows, D, 0, 0, _dtype_code(out),
                                       out.data_ptr(), _stream(o_parts)), "attn_merge_lse")
+    return out
+
+
+def merge_lse_packed(gathered, rows: int, D: int, out):
+    """gathered [parts, rows*(D+1)] fp32: each part is a rank's O [rows, D] followed by its
+    lse [rows] (the buffer one all-gather of decode_partial's packed output produces)."""
+    _dev(gathered, "gathered")
+    parts = gathered.shape[0]
+    stride = rows * (D + 1)
+    base = gathered.data_ptr()
+    _check(lib().b200p_attn_merge_lse(base, base + rows * D * 4, parts, rows, D, stride, stride, _dtype_code(out),
+                                      out.data_ptr(), _stream(gathered)), "attn_merge_lse")
     return out
 
 

@@ -546,23 +546,25 @@ decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict_
 }
 
 // Merge G normalised partials by their lse (KV sequence sharded over G ranks):
-// O = sum_g e^{lse_g - M} O_g / sum_g e^{lse_g - M}.  parts laid out [G][rows][D], [G][rows].
+// O = sum_g e^{lse_g - M} O_g / sum_g e^{lse_g - M}.  Part g starts at o_parts + g*o_stride
+// ([rows][D]) and lse_parts + g*l_stride ([rows]).
 template <typename T, int D>
 __global__ void __launch_bounds__(128)
-merge_lse_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts, int G, int rows, T* __restrict__ o) {
+merge_lse_kernel(const float* __restrict__ o_parts, const float* __restrict__ lse_parts, int G, int rows,
+                 long long o_stride, long long l_stride, T* __restrict__ o) {
     const int row = blockIdx.x * 4 + threadIdx.x / 32, lane = threadIdx.x % 32;
     if (row >= rows) return;
     constexpr int PER = D / 32;
     float M = -INFINITY;
-    for (int g = 0; g < G; ++g) M = fmaxf(M, lse_parts[size_t(g) * rows + row]);
+    for (int g = 0; g < G; ++g) M = fmaxf(M, lse_parts[size_t(g) * l_stride + row]);
     float den = 0.f, acc[PER];
     #pragma unroll
     for (int i = 0; i < PER; ++i) acc[i] = 0.f;
     for (int g = 0; g < G; ++g) {
-        const float w = (M == -INFINITY) ? 0.f : __expf(lse_parts[size_t(g) * rows + row] - M);
+        const float w = (M == -INFINITY) ? 0.f : __expf(lse_parts[size_t(g) * l_stride + row] - M);
         den += w;
         #pragma unroll
-        for (int i = 0; i < PER; ++i) acc[i] += w * o_parts[(size_t(g) * rows + row) * D + lane + 32 * i];
+        for (int i = 0; i < PER; ++i) acc[i] += w * o_parts[size_t(g) * o_stride + size_t(row) * D + lane + 32 * i];
     }
     const float inv = den > 0.f ? 1.f / den : 1.f;
     #pragma unroll
@@ -737,7 +739,10 @@ extern "C" int b200p_attn_decode_partial(const void* q, const void* K, const voi
 }
 
 extern "C" int b200p_attn_merge_lse(const float* o_parts, const float* lse_parts, int parts, int rows, int D,
+                                    long long o_part_stride, long long lse_part_stride,
                                     int dtype, void* o, b200p_stream_t stream) {
+    const long long os = o_part_stride > 0 ? o_part_stride : (long long)rows * D;
+    const long long ls = lse_part_stride > 0 ? lse_part_stride : (long long)rows;
     if (!o_parts || !lse_parts || !o) return B200P_E_NULL;
     if (dtype != B200P_F16 && dtype != B200P_BF16) return B200P_E_DTYPE;
     if (D != 64 && D != 128) return B200P_E_DIM;
@@ -746,11 +751,11 @@ extern "C" int b200p_attn_merge_lse(const float* o_parts, const float* lse_parts
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     const int grid = (rows + 3) / 4;
     if (dtype == B200P_F16) {
-        if (D == 128) merge_lse_kernel<__half, 128><<<grid, 128, 0, st>>>(o_parts, lse_parts, parts, rows, static_cast<__half*>(o));
-        else          merge_lse_kernel<__half, 64><<<grid, 128, 0, st>>>(o_parts, lse_parts, parts, rows, static_cast<__half*>(o));
+        if (D == 128) merge_lse_kernel<__half, 128><<<grid, 128, 0, st>>>(o_parts, lse_parts, parts, rows, os, ls, static_cast<__half*>(o));
+        else          merge_lse_kernel<__half, 64><<<grid, 128, 0, st>>>(o_parts, lse_parts, parts, rows, os, ls, static_cast<__half*>(o));
     } else {
-        if (D == 128) merge_lse_kernel<__nv_bfloat16, 128><<<grid, 128, 0, st>>>(o_parts, lse_parts, parts, rows, static_cast<__nv_bfloat16*>(o));
-        else          merge_lse_kernel<__nv_bfloat16, 64><<<grid, 128, 0, st>>>(o_parts, lse_parts, parts, rows, static_cast<__nv_bfloat16*>(o));
+        if (D == 128) merge_lse_kernel<__nv_bfloat16, 128><<<grid, 128, 0, st>>>(o_parts, lse_parts, parts, rows, os, ls, static_cast<__nv_bfloat16*>(o));
+        else          merge_lse_kernel<__nv_bfloat16, 64><<<grid, 128, 0, st>>>(o_parts, lse_parts, parts, rows, os, ls, static_cast<__nv_bfloat16*>(o));
     }
     return launched();
 }

@@ -10,11 +10,18 @@ K steps timed with CUDA events on the launching stream between a barrier +
 synchronize on both sides; the time is the max over ranks; rank 0 prints ONE
 JSON line.
 
-Workloads
-  segops   segmented wave64 reduce + inclusive-scan sweep over 2^26 elements per
-           dtype: reduce {f32,f64,i32,i64} x {sum,max,min}, reduce {f16,bf16} sum
-           (fp32 accumulation), scan-sum {f32,f64,i32,i64,f16,bf16}.  HBM-bound.
-           N > 1: every rank sweeps its own 2^26-element shard (weak scaling).
+Workloads (default `all`: segops is the headline line, decode and prefill ride along
+under "others", each with its own roofline, e2e and cpu_baseline)
+  segops       segmented wave64 reduce + inclusive-scan sweep over 2^26 elements per
+               dtype: reduce {f32,f64,i32,i64} x {sum,max,min}, reduce {f16,bf16} sum
+               (fp32 accumulation), scan-sum {f32,f64,i32,i64,f16,bf16}.  HBM-bound.
+               N > 1: every rank sweeps its own 2^26-element shard (weak scaling).
+  decode       GQA decode, batch 64, 32 q / 8 kv heads, D 128, 8192 cached keys, bf16.
+               HBM-bound.  N > 1: every rank its own (batch, kv-head) units (weak).
+  prefill      causal prefill, batch 8, 32 heads, seq 4096, D 128, bf16.  Tensor-bound.
+               N > 1: every rank its own (batch, head) units (weak).
+  decode_long  the 131072-key decode with the KV sequence split across the ranks and
+               one NCCL all-gather of (O, lse) per step (strong scaling).
 
 --impl reference times the CPU statement of the same path (the oracle) on the
 host cores, on a bounded sample, in the same metric.
@@ -238,7 +245,7 @@ class DecodeGQA:
         if n:
             self.N = n
         self.bytes_per_step = 2 * self.B * self.NKVH * self.N * self.D * 2 + 2 * self.B * self.NQH * self.D * 2
-        self.cases = [("decode_splitkv_kernel (+ combine)", None, None, None, self.bytes_per_step)]
+        self.cases = [("decode_mma_kernel (+ combine)", None, None, None, self.bytes_per_step)]
 
     def config(self, world):
         return {"workload": "GQA decode (BASELINE config 4)", "batch_per_gpu": self.B, "q_heads": self.NQH, "kv_heads": self.NKVH,
@@ -357,77 +364,150 @@ class PrefillCausal:
     cpu_sample_text = "16 of the 256 (batch, head) units at full sequence length"
 
 
-WORKLOADS = {"segops": SegopsSweep, "decode": DecodeGQA, "prefill": PrefillCausal}
+# --------------------------------------------------------------------------------------
+# workload: long-context decode, KV sequence sharded across the GPUs (strong scaling)
+# --------------------------------------------------------------------------------------
+class DecodeLong:
+    name = "decode_long"
+    metric = "long-context GQA decode attention throughput (algorithmic K/V/q/o bytes)"
+    unit = "GB/s"
+    dtype = "bf16 (fp32 softmax and accumulation)"
+    scaling = "strong"
+    B, NQH, NKVH, D, N = 64, 32, 8, 128, 131072
+
+    def __init__(self, n=None):
+        if n:
+            self.N = n
+        self.total_bytes = 2 * self.B * self.NKVH * self.N * self.D * 2 + 2 * self.B * self.NQH * self.D * 2
+        self.cases = [("decode_mma_kernel + combine (+ all-gather, lse merge)", None, None, None, self.total_bytes)]
+
+    def config(self, world):
+        return {"workload": "long-context GQA decode (BASELINE config 4, 131072-token variant)", "batch": self.B,
+                "q_heads": self.NQH, "kv_heads": self.NKVH, "head_dim": self.D, "kv_len": self.N,
+                "sharding": f"KV sequence in {world} contiguous chunks; one NCCL all-gather of (O, lse) "
+                            f"({self.B * self.NQH * (self.D + 1) * 4} B per rank) + local lse merge" if world > 1
+                            else "single GPU holds the whole KV sequence; no collective",
+                "l2": "K/V shard larger than L2", "e2e": "q H2D + o D2H every step; the KV cache is resident state",
+                "inputs": "q, K, V ~ N(0,1) rounded to bf16, seeded"}
+
+    def setup(self, torch, pkg, device, rank):
+        import torch.distributed as dist
+        import importlib
+        sharding = importlib.import_module(pkg.__name__ + ".sharding")
+        self.torch, self.pkg = torch, pkg
+        world = dist.get_world_size() if dist.is_initialized() else 1
+        self.world = world
+        self.bytes_per_step = self.total_bytes / world        # the generic code multiplies by world
+        self.off, self.len = sharding.kv_shard(self.N, rank, world)
+        g = torch.Generator(device=device); g.manual_seed(0xB214)          # same q on every rank
+        self.q = torch.randn(self.B, self.NQH, self.D, device=device, generator=g).bfloat16()
+        g.manual_seed(0xB214 + 1 + rank)
+        self.K = torch.empty(self.B, self.NKVH, max(self.len, 1), self.D, device=device, dtype=torch.bfloat16)
+        self.V = torch.empty_like(self.K)
+        for b in range(self.B):                                            # per sequence: bounds the fp32 temporaries
+            self.K[b] = torch.randn(self.K.shape[1:], device=device, generator=g).bfloat16()
+            self.V[b] = torch.randn(self.K.shape[1:], device=device, generator=g).bfloat16()
+        self.dec = sharding.LongContextDecoder(pkg, dist if world > 1 else None, self.B, self.NQH, self.D,
+                                               torch.bfloat16, device)
+        self.q_host = self.q.cpu().pin_memory()
+        self.o_host = torch.empty(self.q.shape, dtype=torch.bfloat16).pin_memory()
+        torch.cuda.synchronize()
+
+    def step(self, events=None):
+        self.dec.step(self.q, self.K, self.V, n_keys=self.len)
+        if events is not None:
+            e = self.torch.cuda.Event(enable_timing=True); e.record(); events.append(e)
+
+    def step_e2e(self):
+        self.q.copy_(self.q_host, non_blocking=True)
+        self.step()
+        self.o_host.copy_(self.dec.out, non_blocking=True)
+
+    def e2e_bytes(self):
+        return self.q_host.numel() * 2, self.o_host.numel() * 2
+
+    def cpu_run(self, orc, n, threads, reps=1):
+        """n = sequences; KV length 8192 (1/16 of the workload's) to bound host memory and time."""
+        import numpy as np
+        N = 8192
+        rng = np.random.default_rng(0xB214)
+        q = rng.standard_normal((n, self.NQH, self.D), dtype=np.float32)
+        K = rng.standard_normal((n, self.NKVH, N, self.D), dtype=np.float32)
+        V = rng.standard_normal((n, self.NKVH, N, self.D), dtype=np.float32)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            orc.cpu_decode(q, K, V, self.D, N, self.NQH, self.NKVH, batch=n, threads=threads)
+        dt = (time.perf_counter() - t0) / reps
+        return (2 * n * self.NKVH * N * self.D * 2 + 2 * n * self.NQH * self.D * 2) / dt / 1e9, dt
+
+    cpu_sample = 8
+    cpu_sample_text = "8 sequences x 8192 keys (1/128 of the workload's K/V bytes)"
+
+
+WORKLOADS = {"segops": SegopsSweep, "decode": DecodeGQA, "prefill": PrefillCausal, "decode_long": DecodeLong}
+ALL_ORDER = ["segops", "decode", "prefill"]          # `--workload all`: the first is the headline
+
+
+def make_workload(name, elements=None):
+    return WORKLOADS[name](elements) if elements else WORKLOADS[name]()
 
 
 # --------------------------------------------------------------------------------------
-def reference_arm(args, wl, rank, world):
-    """The CPU statement of the path (oracle) on the host cores; rank 0 only."""
+def cpu_line(wl, orc, steps, budget_s=120.0):
+    """The CPU statement of the workload (oracle) on the host cores: median over `steps`
+    runs of a bounded sample."""
+    threads = orc.hardware_threads()
+    wl.cpu_run(orc, max(1, wl.cpu_sample // 8), threads)
+    vals, t_all = [], time.perf_counter()
+    for _ in range(max(1, steps)):
+        vals.append(wl.cpu_run(orc, wl.cpu_sample, threads))
+        if time.perf_counter() - t_all > budget_s:
+            break
+    v = statistics.median(x[0] for x in vals)
+    dt = statistics.median(x[1] for x in vals)
+    return v, dt, len(vals), threads
+
+
+def reference_arm(args, names, rank, world):
+    """`--impl reference`: the CPU statement of the path on the host cores; rank 0 only."""
     if rank != 0:
         return
     import oracle as orc
-    threads = orc.hardware_threads()
-    sample_n = wl.cpu_sample
-    wl.cpu_run(orc, max(1, sample_n // 8), threads)
-    vals = []
-    t_all = time.perf_counter()
-    for _ in range(args.steps):
-        v, dt = wl.cpu_run(orc, sample_n, threads)
-        vals.append((v, dt))
-        if time.perf_counter() - t_all > 120:
-            break
-    v = statistics.median(x[0] for x in vals)
-    ms = statistics.median(x[1] for x in vals) * 1e3
-    line = {"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus,
-            "steps": len(vals), "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)",
-            "config": wl.config(world),
-            "cpu_baseline": {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
-                             "sample": f"{wl.cpu_sample_text} per step; independent units split over {threads} host threads"},
-            "e2e": {"value": v, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    lines = []
+    for name in names:
+        wl = make_workload(name, args.elements)
+        v, dt, n, threads = cpu_line(wl, orc, args.steps, budget_s=120.0 / len(names))
+        lines.append({"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus,
+                      "steps": n, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+                      "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": wl.dtype,
+                      "data": "synthetic (seeded)", "config": wl.config(world),
+                      "cpu_baseline": {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
+                                       "sample": f"{wl.cpu_sample_text} per step; independent units split over {threads} host threads"},
+                      "e2e": {"value": v, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}})
+    line = lines[0]
+    if len(lines) > 1:
+        line["others"] = lines[1:]
     print(json.dumps(line), flush=True)
 
 
-def main():
-    ap = argparse.ArgumentParser()
-    ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="segops", choices=sorted(WORKLOADS))
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer (end-to-end) measurement")
-    ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--elements", type=int, default=None,
-                    help="elements per dtype (default 2^26); smaller cases are for profiler captures only")
-    args = ap.parse_args()
-
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    wl = WORKLOADS[args.workload](args.elements) if args.elements else WORKLOADS[args.workload]()
-
-    if args.impl == "reference":
-        reference_arm(args, wl, rank, world)
-        return
-
-    import torch
-    import torch.distributed as dist
-    import __graft_entry__ as ge
-    pkg = ge.load_package()
-    pkg.lib()                                   # fail loudly if the CUDA library is missing
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
-    torch.cuda.set_device(local_rank)
-    device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+def measure(wl, args, ctx):
+    """W warm-up steps, K timed steps (device-resident), the end-to-end run, the CPU baseline.
+    Returns the JSON-ready dict (on every rank; rank 0 prints)."""
+    torch, dist, pkg = ctx["torch"], ctx["dist"], ctx["pkg"]
+    device, rank, world, local_rank = ctx["device"], ctx["rank"], ctx["world"], ctx["local_rank"]
+    peaks = ctx["peaks"]
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    peaks = load_peaks()
+    def max_over_ranks(ms):
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
     wl.setup(torch, pkg, device, rank)
     warm = max(args.warmup, 3)
     for _ in range(warm):
@@ -446,32 +526,28 @@ def main():
             wl.step(events)
         barrier()
     launches = pkg.launch_count() - launches0
-    total_ms = events[0].elapsed_time(events[-1])
-    t = torch.tensor([total_ms], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms = float(t.item())
-    ms_per_step = total_ms / args.steps
+    ms_per_step = max_over_ranks(events[0].elapsed_time(events[-1])) / args.steps
     tensor_bound = getattr(wl, "bound", "hbm") == "tensor"
     unit_scale = 1e12 if tensor_bound else 1e9
     peak = peaks["bf16_tflops"] if tensor_bound else peaks["hbm_gbs"]
     value = world * wl.bytes_per_step / (ms_per_step * 1e-3) / unit_scale
 
-    # per-kernel durations (average over the timed steps)
+    # per-kernel durations (average over the timed steps, this rank)
     ncase = len(wl.cases)
     per = [0.0] * ncase
     for s in range(args.steps):
         for i in range(ncase):
             per[i] += events[s * ncase + i].elapsed_time(events[s * ncase + i + 1])
     kernels = []
-    for i, (label, fn, kind, op, nbytes) in enumerate(wl.cases):
+    for i, (label, fn, kind, op, units) in enumerate(wl.cases):
+        units = units / world if getattr(wl, "scaling", "weak") == "strong" else units
         us = max(per[i] / args.steps * 1e3, 1e-3)
-        gbs = nbytes / (us * 1e-6) / unit_scale
-        kernels.append({"kernel": label, "us": round(us, 2), "flops" if tensor_bound else "bytes": nbytes,
-                        wl.unit: round(gbs, 1), "frac": round(gbs / peak, 4)})
+        rate = units / (us * 1e-6) / unit_scale
+        kernels.append({"kernel": label, "us": round(us, 2), "flops" if tensor_bound else "bytes": units,
+                        wl.unit: round(rate, 1), "frac": round(rate / peak, 4)})
     dom = max(range(ncase), key=lambda i: per[i])
-    roofline = {"bound": "tensor" if tensor_bound else "hbm", "kernel": kernels[dom]["kernel"], "achieved": kernels[dom][wl.unit],
-                "peak": peak, "unit": wl.unit, "frac": kernels[dom]["frac"],
+    roofline = {"bound": "tensor" if tensor_bound else "hbm", "kernel": kernels[dom]["kernel"],
+                "achieved": kernels[dom][wl.unit], "peak": peak, "unit": wl.unit, "frac": kernels[dom]["frac"],
                 "peak_source": f"{peaks['source']} " + ("cuBLAS bf16 burst" if tensor_bound else "copy bandwidth"),
                 "traffic": TRAFFIC.get(kernels[dom]["kernel"])}
 
@@ -485,10 +561,7 @@ def main():
         wl.step_e2e()
     e1.record()
     barrier()
-    t = torch.tensor([e0.elapsed_time(e1)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    e2e_ms = float(t.item()) / e2e_steps
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
     h2d, d2h = wl.e2e_bytes()
     e2e = {"value": world * wl.bytes_per_step / (e2e_ms * 1e-3) / unit_scale, "unit": wl.unit, "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps}
@@ -497,18 +570,65 @@ def main():
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle as orc
-        threads = orc.hardware_threads()
-        wl.cpu_run(orc, max(1, wl.cpu_sample // 8), threads)
-        v, dt = wl.cpu_run(orc, wl.cpu_sample, threads, reps=3)
+        v, dt, n, threads = cpu_line(wl, orc, 3, budget_s=30.0)
         cpu = {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
-               "sample": f"{wl.cpu_sample_text}, 3 repetitions, {dt:.2f} s each; independent units split over {threads} host threads"}
+               "sample": f"{wl.cpu_sample_text}, median of {n} runs of {dt:.2f} s; independent units split over {threads} host threads"}
 
+    return {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+            "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": wl.dtype,
+            "data": "synthetic (seeded)", "config": wl.config(world), "clocks": clk.summary(), "e2e": e2e,
+            "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu, "kernels": kernels}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--workload", default="all", choices=sorted(WORKLOADS) + ["all"],
+                    help="all = segops (headline) with decode and prefill reported under 'others'")
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer (end-to-end) measurement")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--elements", type=int, default=None,
+                    help="problem size override (elements per dtype / kv length / seq length); "
+                         "smaller cases are for profiler captures only")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    names = ALL_ORDER if args.workload == "all" else [args.workload]
+
+    if args.impl == "reference":
+        reference_arm(args, names, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+    import __graft_entry__ as ge
+    pkg = ge.load_package()
+    pkg.lib()                                   # fail loudly if the CUDA library is missing
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: there is no CPU path")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")      # stdout carries exactly one JSON line
+        dist.init_process_group("nccl", device_id=device)
+    ctx = {"torch": torch, "dist": dist, "pkg": pkg, "device": device, "rank": rank, "world": world,
+           "local_rank": local_rank, "peaks": load_peaks()}
+    lines = []
+    for name in names:
+        wl = make_workload(name, args.elements)
+        lines.append(measure(wl, args, ctx))
+        del wl
+        torch.cuda.empty_cache()
     if rank == 0:
-        line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-                "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
-                "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic (seeded)", "config": wl.config(world),
-                "clocks": clk.summary(), "e2e": e2e, "gpu_launches": launches, "roofline": roofline,
-                "cpu_baseline": cpu, "kernels": kernels}
+        line = lines[0]
+        if len(lines) > 1:
+            line["others"] = lines[1:]
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -147,10 +147,14 @@ int b200p_attn_decode_partial(const void* q, const void* K, const void* V, float
                               const b200p_decode_args* args, void* workspace, size_t workspace_bytes,
                               b200p_stream_t stream);
 
-/* Merge `parts` shard results: o_parts [parts, rows, D] fp32, lse_parts
- * [parts, rows] -> o [rows, D] in `dtype`.
+/* Merge `parts` shard results -> o [rows, D] in `dtype`.  Part g is
+ * o_parts + g*o_part_stride ([rows, D] fp32) and lse_parts + g*lse_part_stride
+ * ([rows]); a stride of 0 means densely packed parts.  With both strides equal
+ * to rows*(D+1) the parts can be the rows of ONE all-gathered buffer that holds
+ * each rank's O followed by its lse.
  * O = sum_g e^{lse_g-M} O_g / sum_g e^{lse_g-M} (fa_decode_kernel.hpp:75-92). */
 int b200p_attn_merge_lse(const float* o_parts, const float* lse_parts, int parts, int rows, int D,
+                         long long o_part_stride, long long lse_part_stride,
                          int dtype, void* o, b200p_stream_t stream);
 
 /* Decode for callers that cannot supply scratch memory -- a serving loop whose
