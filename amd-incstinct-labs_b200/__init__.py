@@ -40,8 +40,16 @@ SYMBOLS = {
     "b200p_attn_decode_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "b200p_attn_decode_noalloc_max_bytes": (_sz, []),
     "b200p_attn_prefill": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp]),
+    "b200p_attn_prefill_strided": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
     "b200p_attn_prefill_debug": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, _vp]),
     "b200p_device_status": (_i, [_i]),
+    "b200p_session_create": (_vp, [_vp, _i, _i, _vp]),
+    "b200p_session_destroy": (None, [_vp]),
+    "b200p_session_generate": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp]),
+    "b200p_session_prefill_logits": (_i, [_vp, _vp, _i, _vp, _vp]),
+    "b200p_session_step_logits": (_i, [_vp, _vp, _vp, _vp]),
+    "b200p_session_kv_len": (_i, [_vp]),
+    "b200p_session_gemm_calls": (C.c_ulonglong, [_vp]),
     "b200p_fa_step": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.c_float, _vp]),
 }
 
@@ -54,7 +62,8 @@ class PrefillCfg(C.Structure):
 class DecodeArgs(C.Structure):
     """struct b200p_decode_args (include/b200p.h)."""
     _fields_ = [("D", _i), ("N", _i), ("nQHeads", _i), ("nKVHeads", _i), ("stride_kv", _i), ("batch", _i),
-                ("dtype", _i), ("kv_batch_stride", _ll), ("key_offset", _ll)]
+                ("dtype", _i), ("kv_batch_stride", _ll), ("key_offset", _ll), ("q_batch_stride", _ll),
+                ("o_batch_stride", _ll)]
 
 
 class B200PError(RuntimeError):
@@ -170,7 +179,7 @@ def _decode_args(q, K, N, key_offset):
     batch, nQH, D = q.shape
     _, nKVH, stride_kv, _ = K.shape
     N = stride_kv - key_offset if N is None else N
-    a = DecodeArgs(D, N, nQH, nKVH, stride_kv, batch, _dtype_code(q), K.stride(0), key_offset)
+    a = DecodeArgs(D, N, nQH, nKVH, stride_kv, batch, _dtype_code(q), K.stride(0), key_offset, q.stride(0), 0)
     return a, batch, nQH, D
 
 
@@ -285,6 +294,30 @@ def prefill(Q, K, V, causal: bool = False, out=None, raw_scores=None):
     return out
 
 
+class AttnStrides(C.Structure):
+    """struct b200p_attn_strides: (token, head, sequence) element strides of Q, K, V, O."""
+    _fields_ = [(n, _ll) for n in ("q_seq", "q_head", "q_batch", "k_seq", "k_head", "k_batch",
+                                   "v_seq", "v_head", "v_batch", "o_seq", "o_head", "o_batch")]
+
+
+def prefill_strided(Q, K, V, O, causal: bool = False):
+    """prefill() on 4-D views [batch, heads, seq, D] with arbitrary (8-element aligned)
+    strides, e.g. a permuted token-major projection or a slice of a KV cache; D contiguous."""
+    for t, n in ((Q, "Q"), (K, "K"), (V, "V"), (O, "O")):
+        if not t.is_cuda:
+            raise ValueError(f"{n} must be a CUDA tensor: there is no CPU path")
+        if t.stride(3) != 1:
+            raise ValueError(f"{n}: the head dimension must be contiguous")
+    batch, nQH, seqQ, D = Q.shape
+    _, nKVH, seqK, _ = K.shape
+    cfg = PrefillCfg(D, seqQ, seqK, nQH, nKVH, batch, int(causal))
+    st = AttnStrides(Q.stride(2), Q.stride(1), Q.stride(0), K.stride(2), K.stride(1), K.stride(0),
+                     V.stride(2), V.stride(1), V.stride(0), O.stride(2), O.stride(1), O.stride(0))
+    _check(lib().b200p_attn_prefill_strided(Q.data_ptr(), K.data_ptr(), V.data_ptr(), O.data_ptr(), C.byref(cfg),
+                                            _dtype_code(Q), C.byref(st), _stream(Q)), "attn_prefill_strided")
+    return O
+
+
 def device_status(clear: bool = True) -> int:
     """0, or B200P_E_TIMEOUT if a kernel abandoned a bounded wait (synchronises the device)."""
     return int(lib().b200p_device_status(int(clear)))
@@ -306,3 +339,100 @@ def fa_step(step: str, Q, K, V, scale: float = 0.0, out=None):
     _check(lib().b200p_fa_step(FA_STEPS[step], _dtype_code(Q), Q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(),
                                batch, heads, sq, sk, D, float(scale), _stream(Q)), "fa_step")
     return out
+
+
+# ---- the small LLM runtime (cdna3::runtime::Session) --------------------------------------------
+class ModelConfig(C.Structure):
+    """struct b200p_model_config == cdna3::runtime::ModelConfig."""
+    _fields_ = [("n_layers", _i), ("hidden", _i), ("n_heads", _i), ("n_kv_heads", _i), ("head_dim", _i),
+                ("ffn_dim", _i), ("vocab_size", _i), ("rope_theta", C.c_float)]
+
+
+_LAYER_FIELDS = ("Wq", "Wk", "Wv", "Wo", "bq", "bk", "bv", "Wgate", "Wup", "Wdown", "norm_attn", "norm_mlp")
+
+
+class LayerWeights(C.Structure):
+    _fields_ = [(n, _vp) for n in _LAYER_FIELDS]
+
+
+class ModelWeights(C.Structure):
+    _fields_ = [("cfg", ModelConfig), ("dtype", _i), ("embed_tokens", _vp), ("lm_head", _vp), ("final_norm", _vp),
+                ("layers", C.POINTER(LayerWeights))]
+
+
+class Session:
+    """Greedy-decoding session over caller-owned weights.
+
+    weights: {"embed_tokens", "lm_head", "final_norm": tensors, "layers": [ {Wq, Wk, Wv, Wo, Wgate, Wup, Wdown,
+    norm_attn, norm_mlp[, bq, bk, bv]} ... ]}, all CUDA tensors of one 16-bit dtype, nn.Linear layout [out, in].
+    cfg: dict with the ModelConfig fields.  The session keeps the tensors alive."""
+
+    def __init__(self, cfg: dict, weights: dict, max_seq: int, batch: int):
+        self._weights = weights
+        self.cfg, self.batch, self.max_seq = dict(cfg), batch, max_seq
+        layers = (LayerWeights * cfg["n_layers"])()
+        for i, lw in enumerate(weights["layers"]):
+            for n in _LAYER_FIELDS:
+                t = lw.get(n)
+                setattr(layers[i], n, _dev(t, n).data_ptr() if t is not None else None)
+        self._layers = layers
+        mc = ModelConfig(cfg["n_layers"], cfg["hidden"], cfg["n_heads"], cfg["n_kv_heads"], cfg["head_dim"],
+                         cfg["ffn_dim"], cfg["vocab_size"], float(cfg.get("rope_theta", 10000.0)))
+        mw = ModelWeights(mc, _dtype_code(weights["embed_tokens"]), _dev(weights["embed_tokens"], "embed_tokens").data_ptr(),
+                          _dev(weights["lm_head"], "lm_head").data_ptr(), _dev(weights["final_norm"], "final_norm").data_ptr(),
+                          layers)
+        st = _i(0)
+        self._h = lib().b200p_session_create(C.byref(mw), max_seq, batch, C.byref(st))
+        if not self._h:
+            raise B200PError(st.value, "session_create")
+        self._device = weights["embed_tokens"].device
+
+    def close(self):
+        if getattr(self, "_h", None):
+            lib().b200p_session_destroy(self._h)
+            self._h = None
+
+    __del__ = close
+
+    def _ids(self, ids):
+        import numpy as np
+        a = np.ascontiguousarray(ids, dtype=np.int32)
+        return a
+
+    def generate(self, input_ids, max_new_tokens: int):
+        """input_ids [batch, T] (host ints) -> (tokens [batch, max_new_tokens] numpy int32,
+        (ttft_ms, decode_ms))."""
+        import numpy as np
+        import torch
+        a = self._ids(input_ids).reshape(self.batch, -1)
+        out = np.zeros((self.batch, max_new_tokens), np.int32)
+        tm = (C.c_float * 2)()
+        _check(lib().b200p_session_generate(self._h, a.ctypes.data, a.shape[1], max_new_tokens, out.ctypes.data, tm,
+                                            torch.cuda.current_stream(self._device).cuda_stream), "session_generate")
+        return out, (tm[0], tm[1])
+
+    def prefill_logits(self, input_ids):
+        import numpy as np
+        import torch
+        a = self._ids(input_ids).reshape(self.batch, -1)
+        out = np.zeros((self.batch, self.cfg["vocab_size"]), np.float32)
+        _check(lib().b200p_session_prefill_logits(self._h, a.ctypes.data, a.shape[1], out.ctypes.data,
+                                                  torch.cuda.current_stream(self._device).cuda_stream), "session_prefill_logits")
+        return out
+
+    def step_logits(self, token_ids):
+        import numpy as np
+        import torch
+        a = self._ids(token_ids).reshape(self.batch)
+        out = np.zeros((self.batch, self.cfg["vocab_size"]), np.float32)
+        _check(lib().b200p_session_step_logits(self._h, a.ctypes.data, out.ctypes.data,
+                                               torch.cuda.current_stream(self._device).cuda_stream), "session_step_logits")
+        return out
+
+    @property
+    def kv_len(self) -> int:
+        return int(lib().b200p_session_kv_len(self._h))
+
+    @property
+    def gemm_calls(self) -> int:
+        return int(lib().b200p_session_gemm_calls(self._h))

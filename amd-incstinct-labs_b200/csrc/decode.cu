@@ -65,6 +65,7 @@ struct DecodeParams {
     long long kv_head_stride;     // elements between KV heads   (stride_kv * D)
     long long kv_batch_stride;    // elements between sequences
     long long key_offset;         // first key of this launch inside each head (KV shards)
+    long long q_batch_stride;     // elements between sequences in q
     float scale_log2;             // log2(e) / sqrt(D)
 };
 
@@ -153,7 +154,7 @@ decode_splitkv_kernel(const DecodeParams p) {
         #pragma unroll
         for (int h = 0; h < GH; ++h) {
             const bool live = h0 + h < p.group;
-            const T* qp = static_cast<const T*>(p.q) + (size_t(b) * p.nQH + size_t(kvh) * p.group + (live ? h0 + h : 0)) * D;
+            const T* qp = static_cast<const T*>(p.q) + size_t(b) * p.q_batch_stride + (size_t(kvh) * p.group + (live ? h0 + h : 0)) * D;
             #pragma unroll
             for (int c = 0; c < CH; ++c) {
                 #pragma unroll
@@ -385,7 +386,7 @@ decode_mma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK
         // Q fragments: rows g and g+8 are heads of the group (zero past it)
         uint32_t qa[KS][4];
         {
-            const T* qbase = static_cast<const T*>(p.q) + (size_t(b) * p.nQH + size_t(kvh) * p.group) * D;
+            const T* qbase = static_cast<const T*>(p.q) + size_t(b) * p.q_batch_stride + size_t(kvh) * p.group * D;
             const bool v0 = g < p.group, v1 = g + 8 < p.group;
             const uint32_t* r0 = reinterpret_cast<const uint32_t*>(qbase + size_t(v0 ? g : 0) * D);
             const uint32_t* r1 = reinterpret_cast<const uint32_t*>(qbase + size_t(v1 ? g + 8 : 0) * D);
@@ -520,6 +521,7 @@ decode_mma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK
 template <typename T, int D, int MODE>
 __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits, int rows,
+                      int rows_per_seq, long long o_batch_stride,
                       T* __restrict__ o, float* __restrict__ o_f32, float* __restrict__ lse) {
     const int row = blockIdx.x * 4 + threadIdx.x / 32, lane = threadIdx.x % 32;
     if (row >= rows) return;
@@ -539,7 +541,7 @@ decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict_
     #pragma unroll
     for (int i = 0; i < PER; ++i) {
         const float v = acc[i] * inv;
-        if (MODE == 0) o[size_t(row) * D + lane + 32 * i] = from_float<T>(v);
+        if (MODE == 0) o[size_t(row / rows_per_seq) * o_batch_stride + size_t(row % rows_per_seq) * D + lane + 32 * i] = from_float<T>(v);
         else           o_f32[size_t(row) * D + lane + 32 * i] = v;
     }
     if (MODE == 1 && lane == 0) lse[row] = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
@@ -667,10 +669,11 @@ int launch_decode_mma_d(const DecodeParams& p, const b200p_decode_args* a, cudaS
 }
 
 template <typename T, int D>
-int launch_combine(const float* po, const float* pml, int splits, int rows, void* o, float* o32, float* lse, cudaStream_t st) {
+int launch_combine(const float* po, const float* pml, int splits, int rows, int rows_per_seq, long long o_bs,
+                   void* o, float* o32, float* lse, cudaStream_t st) {
     const int grid = (rows + 3) / 4;
-    if (o) decode_combine_kernel<T, D, 0><<<grid, 128, 0, st>>>(po, pml, splits, rows, static_cast<T*>(o), nullptr, nullptr);
-    else   decode_combine_kernel<T, D, 1><<<grid, 128, 0, st>>>(po, pml, splits, rows, nullptr, o32, lse);
+    if (o) decode_combine_kernel<T, D, 0><<<grid, 128, 0, st>>>(po, pml, splits, rows, rows_per_seq, o_bs, static_cast<T*>(o), nullptr, nullptr);
+    else   decode_combine_kernel<T, D, 1><<<grid, 128, 0, st>>>(po, pml, splits, rows, rows_per_seq, o_bs, nullptr, o32, lse);
     return launched();
 }
 
@@ -693,6 +696,8 @@ int run_decode(const b200p_decode_args* a, const void* q, const void* K, const v
     p.kv_head_stride = (long long)a->stride_kv * a->D;
     p.kv_batch_stride = a->kv_batch_stride > 0 ? a->kv_batch_stride : (long long)a->nKVHeads * a->stride_kv * a->D;
     p.key_offset = a->key_offset;
+    p.q_batch_stride = a->q_batch_stride > 0 ? a->q_batch_stride : (long long)a->nQHeads * a->D;
+    if (p.q_batch_stride % 2) return B200P_E_ALIGN;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(a->D));
     // K/V rows must start on 16 bytes for the bulk copies
     if ((p.kv_head_stride * 2) % 16 || (p.kv_batch_stride * 2) % 16) return B200P_E_ALIGN;
@@ -706,12 +711,13 @@ int run_decode(const b200p_decode_args* a, const void* q, const void* K, const v
     if (use_mma) e = a->dtype == B200P_F16 ? launch_decode_mma_d<__half>(p, a, st) : launch_decode_mma_d<__nv_bfloat16>(p, a, st);
     else         e = a->dtype == B200P_F16 ? launch_decode_d<__half>(p, a->D, st) : launch_decode_d<__nv_bfloat16>(p, a->D, st);
     if (e) return e;
-    const int rows = a->batch * a->nQHeads;
+    const int rows = a->batch * a->nQHeads, rps = a->nQHeads;
+    const long long obs = a->o_batch_stride > 0 ? a->o_batch_stride : (long long)a->nQHeads * a->D;
     if (a->dtype == B200P_F16)
-        return a->D == 128 ? launch_combine<__half, 128>(p.part_o, p.part_ml, pl.splits, rows, o, o_f32, lse, st)
-                           : launch_combine<__half, 64>(p.part_o, p.part_ml, pl.splits, rows, o, o_f32, lse, st);
-    return a->D == 128 ? launch_combine<__nv_bfloat16, 128>(p.part_o, p.part_ml, pl.splits, rows, o, o_f32, lse, st)
-                       : launch_combine<__nv_bfloat16, 64>(p.part_o, p.part_ml, pl.splits, rows, o, o_f32, lse, st);
+        return a->D == 128 ? launch_combine<__half, 128>(p.part_o, p.part_ml, pl.splits, rows, rps, obs, o, o_f32, lse, st)
+                           : launch_combine<__half, 64>(p.part_o, p.part_ml, pl.splits, rows, rps, obs, o, o_f32, lse, st);
+    return a->D == 128 ? launch_combine<__nv_bfloat16, 128>(p.part_o, p.part_ml, pl.splits, rows, rps, obs, o, o_f32, lse, st)
+                       : launch_combine<__nv_bfloat16, 64>(p.part_o, p.part_ml, pl.splits, rows, rps, obs, o, o_f32, lse, st);
 }
 
 } // namespace

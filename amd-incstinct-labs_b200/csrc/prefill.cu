@@ -58,7 +58,7 @@ namespace {
 
 constexpr int kBM = 128;                 // query rows per tile
 constexpr int kBN = 128;                 // keys per tile
-constexpr int kPrefillThreads = 320;     // 2 softmax warpgroups + MMA warp + TMA warp
+constexpr int kPrefillThreads = 384;     // 2 softmax warpgroups + a warpgroup holding the MMA and TMA warps
 constexpr int kMmaWarp = 8, kTmaWarp = 9;
 constexpr float kLazyRescale = 8.0f;     // log2 units
 
@@ -77,6 +77,7 @@ template <int D> struct PrefillShape {
 
 struct PrefillParams {
     void* O;
+    long long o_seq, o_head, o_batch;   // element strides of O
     float* debug_s;            // optional: raw S of tile (0,0) of CTA (0,0,0), [128][128] fp32
     int seqQ, seqK, nQH, nKVH, group, batch, causal;
     float scale_log2;
@@ -136,7 +137,12 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     const uint32_t tmem = s_tmem_base;
     const uint32_t sm_q = dme::smem_addr(smem + Sh::OFF_Q), sm_k = dme::smem_addr(smem + Sh::OFF_K), sm_v = dme::smem_addr(smem + Sh::OFF_V);
 
-    if (warp == kTmaWarp) {
+    // Register budget: the softmax warpgroups hold a whole 128-column score row per thread, the
+    // MMA / TMA warpgroup needs very little; 128 * (224 + 224 + 56) = 64512 <= 65536.
+    // (Each role branch opens with its own setmaxnreg, so the compiler sees one limit per branch.)
+    if (warp >= 8) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+      if (warp == kTmaWarp) {
         // ---------------------------------- TMA producer ----------------------------------
         if (lane == 0) {
             dme::prefetch_tensor_map(&mapQ); dme::prefetch_tensor_map(&mapK); dme::prefetch_tensor_map(&mapV);
@@ -158,26 +164,31 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                 vr.advance();
             }
         }
-    } else if (warp == kMmaWarp) {
+      } else if (warp == kMmaWarp) {
         // ---------------------------------- MMA issuer ------------------------------------
         if (lane == 0) {
             constexpr uint32_t idesc_qk = tc::instr_desc_f16(kBM, kBN, Fmt<T>::id, 0, 0);
             constexpr uint32_t idesc_pv = tc::instr_desc_f16(kBM, D, Fmt<T>::id, 0, 1);
+            // Descriptors differ from a per-tile base only in the 14-bit start-address field
+            // (units of 16 bytes), so a k-step is an integer add on the base.  The k loops are kept
+            // rolled: this warp has few registers and issues 8 instructions per ~500 tensor cycles.
+            const uint64_t q_base = tc::smem_desc_sw128(sm_q, 16, 1024);
+            const uint64_t k_base = tc::smem_desc_sw128(sm_k, 16, 1024);
+            const uint64_t v_base = tc::smem_desc_sw128(sm_v, Sh::SUB_BYTES, 1024);
             auto issue_qk = [&](int t, int kstage) {
-                #pragma unroll
+                const uint64_t qd = q_base + uint64_t((t * Sh::TILE_BYTES) >> 4);
+                const uint64_t kd = k_base + uint64_t((kstage * Sh::TILE_BYTES) >> 4);
+                #pragma unroll 1
                 for (int ks = 0; ks < D / 16; ++ks) {
-                    const uint32_t off = uint32_t(ks / 4) * Sh::SUB_BYTES + uint32_t(ks % 4) * 32u;
-                    tc::mma_ss(tmem + t * kBN,
-                               tc::smem_desc_sw128(sm_q + t * Sh::TILE_BYTES + off, 16, 1024),
-                               tc::smem_desc_sw128(sm_k + kstage * Sh::TILE_BYTES + off, 16, 1024),
-                               idesc_qk, ks > 0);
+                    const uint32_t off16 = (uint32_t(ks >> 2) * Sh::SUB_BYTES + uint32_t(ks & 3) * 32u) >> 4;
+                    tc::mma_ss(tmem + t * kBN, qd + off16, kd + off16, idesc_qk, ks > 0);
                 }
             };
             auto issue_pv = [&](int t, int vstage, bool first) {
-                #pragma unroll
+                const uint64_t vd = v_base + uint64_t((vstage * Sh::TILE_BYTES) >> 4);
+                #pragma unroll 1
                 for (int kk = 0; kk < kBN / 16; ++kk)
-                    tc::mma_ts(tmem + 256 + t * 128, tmem + t * kBN + kk * 8,
-                               tc::smem_desc_sw128(sm_v + vstage * Sh::TILE_BYTES + kk * 2048, Sh::SUB_BYTES, 1024),
+                    tc::mma_ts(tmem + 256 + t * 128, tmem + t * kBN + kk * 8, vd + uint64_t(kk * (2048 >> 4)),
                                idesc_pv, !(first && kk == 0));
             };
             bool ok = dme::wait(q_full, 0);
@@ -210,7 +221,9 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             }
             if (!ok) atomicExch(&s_failed, 1);
         }
+      }
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
         // ---------------------------------- softmax warpgroups ----------------------------
         const int t = warp / 4;                               // query tile of this warpgroup
         const int r = threadIdx.x % kBM;                      // row inside the tile = TMEM lane
@@ -225,24 +238,26 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             tc::fence_after_sync();
             const bool need_mask = (p.causal && j * kBN + kBN - 1 > q0[t]) || (j * kBN + kBN > p.seqK);
             const int col_limit = min(p.causal ? row : 0x7fffffff, p.seqK - 1) - j * kBN;   // columns <= col_limit are live
-            // ---- pass 1: row max -------------------------------------------------------
-            float mx = -INFINITY;
+            // ---- the whole score row into registers (one wait for the four loads) ------------
+            uint32_t sv[kBN];
             #pragma unroll
-            for (int c = 0; c < kBN / 32; ++c) {
-                uint32_t v[32];
-                tc::ld_32x32b_x32(tS + c * 32, v);
-                tc::wait_ld();
-                if (p.debug_s && j == 0 && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
-                    #pragma unroll
-                    for (int i = 0; i < 32; ++i) p.debug_s[r * kBN + c * 32 + i] = __uint_as_float(v[i]);
-                }
+            for (int c = 0; c < kBN / 32; ++c) tc::ld_32x32b_x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
+            tc::wait_ld();
+            if (p.debug_s && j == 0 && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
                 #pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(v[i]);
-                    if (need_mask && c * 32 + i > col_limit) s = -INFINITY;
-                    mx = fmaxf(mx, s);
-                }
+                for (int i = 0; i < kBN; ++i) p.debug_s[r * kBN + i] = __uint_as_float(sv[i]);
             }
+            if (need_mask) {
+                #pragma unroll
+                for (int i = 0; i < kBN; ++i) if (i > col_limit) sv[i] = 0xff800000u;      // -inf
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            #pragma unroll
+            for (int i = 0; i < kBN; i += 4) {
+                #pragma unroll
+                for (int u = 0; u < 4; ++u) mx4[u] = fmaxf(mx4[u], __uint_as_float(sv[i + u]));
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = mx * p.scale_log2;
             float alpha = 1.f;
             if (m_new > m_used + kLazyRescale) { alpha = fast_exp2(m_used - m_new); m_used = m_new; }
@@ -259,28 +274,22 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                 }
                 tc::wait_st();
             }
-            // ---- pass 2: P = exp2(S * scale - m), 16-bit pairs over the front of S ---------
-            float l_add = 0.f;
+            // ---- P = exp2(S * scale - m) as 16-bit pairs over the front of S -------------------
+            const float neg_m = -m_used;
+            float la[4] = {0.f, 0.f, 0.f, 0.f};
             #pragma unroll
             for (int c = 0; c < kBN / 32; ++c) {
-                uint32_t v[32];
-                tc::ld_32x32b_x32(tS + c * 32, v);
-                tc::wait_ld();
                 uint32_t pk[16];
                 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    float s0 = __uint_as_float(v[2 * i]), s1 = __uint_as_float(v[2 * i + 1]);
-                    if (need_mask) {
-                        if (c * 32 + 2 * i > col_limit) s0 = -INFINITY;
-                        if (c * 32 + 2 * i + 1 > col_limit) s1 = -INFINITY;
-                    }
-                    const float p0 = fast_exp2(fmaf(s0, p.scale_log2, -m_used));
-                    const float p1 = fast_exp2(fmaf(s1, p.scale_log2, -m_used));
-                    l_add += p0 + p1;
+                    const float p0 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + 2 * i]), p.scale_log2, neg_m));
+                    const float p1 = fast_exp2(fmaf(__uint_as_float(sv[c * 32 + 2 * i + 1]), p.scale_log2, neg_m));
+                    la[(2 * i) & 3] += p0; la[(2 * i + 1) & 3] += p1;
                     pk[i] = pack2<T>(p0, p1);
                 }
                 tc::st_32x32b_x16(tS + c * 16, pk);
             }
+            const float l_add = (la[0] + la[1]) + (la[2] + la[3]);
             tc::wait_st();
             l = l * alpha + l_add;
             tc::fence_before_sync();
@@ -291,7 +300,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             if (dme::wait(&o_done[t], 0)) {
                 tc::fence_after_sync();
                 const float inv = l > 0.f ? 1.f / l : 1.f;
-                T* orow = static_cast<T*>(p.O) + ((size_t(b) * p.nQH + head) * p.seqQ + row) * D;
+                T* orow = static_cast<T*>(p.O) + size_t(b) * p.o_batch + size_t(head) * p.o_head + size_t(row) * p.o_seq;
                 #pragma unroll
                 for (int c = 0; c < D / 32; ++c) {
                     uint32_t v[32];
@@ -322,18 +331,19 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
 
 template <typename T, int D>
 int launch_prefill(const void* Q, const void* K, const void* V, void* O, const b200p_prefill_cfg* c, int dtype,
-                   float* debug_s, cudaStream_t st) {
+                   const b200p_attn_strides& s, float* debug_s, cudaStream_t st) {
     using Sh = PrefillShape<D>;
     const CUtensorMapDataType dt = dtype == B200P_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
     CUtensorMap mq, mk, mv;
     const uint64_t qd[4] = {uint64_t(D), uint64_t(c->seqQ), uint64_t(c->nQHeads), uint64_t(c->batch)};
-    const uint64_t qs[3] = {uint64_t(D) * 2, uint64_t(c->seqQ) * D * 2, uint64_t(c->nQHeads) * c->seqQ * D * 2};
+    const uint64_t qs[3] = {uint64_t(s.q_seq) * 2, uint64_t(s.q_head) * 2, uint64_t(s.q_batch) * 2};
     const uint64_t kd[4] = {uint64_t(D), uint64_t(c->seqK), uint64_t(c->nKVHeads), uint64_t(c->batch)};
-    const uint64_t ks[3] = {uint64_t(D) * 2, uint64_t(c->seqK) * D * 2, uint64_t(c->nKVHeads) * c->seqK * D * 2};
+    const uint64_t ks[3] = {uint64_t(s.k_seq) * 2, uint64_t(s.k_head) * 2, uint64_t(s.k_batch) * 2};
+    const uint64_t vs[3] = {uint64_t(s.v_seq) * 2, uint64_t(s.v_head) * 2, uint64_t(s.v_batch) * 2};
     const uint32_t box[4] = {64, 128, 1, 1};
     cudaError_t e = make_tensor_map(&mq, dt, 4, Q, qd, qs, box, Swizzle::B128);
     if (e == cudaSuccess) e = make_tensor_map(&mk, dt, 4, K, kd, ks, box, Swizzle::B128);
-    if (e == cudaSuccess) e = make_tensor_map(&mv, dt, 4, V, kd, ks, box, Swizzle::B128);
+    if (e == cudaSuccess) e = make_tensor_map(&mv, dt, 4, V, kd, vs, box, Swizzle::B128);
     if (e != cudaSuccess) return int(e);
 
     auto kern = prefill_tc_kernel<T, D>;
@@ -346,6 +356,7 @@ int launch_prefill(const void* Q, const void* K, const void* V, void* O, const b
     }
     PrefillParams p{};
     p.O = O; p.debug_s = debug_s;
+    p.o_seq = s.o_seq; p.o_head = s.o_head; p.o_batch = s.o_batch;
     p.seqQ = c->seqQ; p.seqK = c->seqK; p.nQH = c->nQHeads; p.nKVH = c->nKVHeads; p.group = c->nQHeads / c->nKVHeads;
     p.batch = c->batch; p.causal = c->causal;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(D));
@@ -356,8 +367,16 @@ int launch_prefill(const void* Q, const void* K, const void* V, void* O, const b
 
 } // namespace
 
+int prefill_dispatch_strided(const void* Q, const void* K, const void* V, void* O, const b200p_prefill_cfg* c, int dtype,
+                             const b200p_attn_strides* strides, float* debug_s, cudaStream_t st);
+
 int prefill_dispatch(const void* Q, const void* K, const void* V, void* O, const b200p_prefill_cfg* c, int dtype,
                      float* debug_s, cudaStream_t st) {
+    return prefill_dispatch_strided(Q, K, V, O, c, dtype, nullptr, debug_s, st);
+}
+
+int prefill_dispatch_strided(const void* Q, const void* K, const void* V, void* O, const b200p_prefill_cfg* c, int dtype,
+                             const b200p_attn_strides* strides, float* debug_s, cudaStream_t st) {
     if (!c) return B200P_E_NULL;
     if (dtype != B200P_F16 && dtype != B200P_BF16) return B200P_E_DTYPE;
     if (c->D != 64 && c->D != 128) return B200P_E_DIM;                        // attention.hpp:105-107
@@ -367,11 +386,25 @@ int prefill_dispatch(const void* Q, const void* K, const void* V, void* O, const
     if (!Q || !K || !V || !O) return B200P_E_NULL;
     if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16)) return B200P_E_ALIGN;
     if (sm_count() <= 0) return B200P_E_NO_DEVICE;
+    b200p_attn_strides s;
+    if (strides) {
+        s = *strides;
+        // TMA needs 16-byte multiples for every stride; the output rows are written with 16-byte stores
+        const long long all[12] = {s.q_seq, s.q_head, s.q_batch, s.k_seq, s.k_head, s.k_batch,
+                                   s.v_seq, s.v_head, s.v_batch, s.o_seq, s.o_head, s.o_batch};
+        for (long long v : all) if (v <= 0 || (v * 2) % 16 != 0) return B200P_E_ALIGN;
+    } else {                                                   // the reference's dense head-major layout
+        const long long D = c->D;
+        s.q_seq = D; s.q_head = (long long)c->seqQ * D; s.q_batch = (long long)c->nQHeads * c->seqQ * D;
+        s.k_seq = D; s.k_head = (long long)c->seqK * D; s.k_batch = (long long)c->nKVHeads * c->seqK * D;
+        s.v_seq = s.k_seq; s.v_head = s.k_head; s.v_batch = s.k_batch;
+        s.o_seq = s.q_seq; s.o_head = s.q_head; s.o_batch = s.q_batch;
+    }
     if (dtype == B200P_F16)
-        return c->D == 128 ? launch_prefill<__half, 128>(Q, K, V, O, c, dtype, debug_s, st)
-                           : launch_prefill<__half, 64>(Q, K, V, O, c, dtype, debug_s, st);
-    return c->D == 128 ? launch_prefill<__nv_bfloat16, 128>(Q, K, V, O, c, dtype, debug_s, st)
-                       : launch_prefill<__nv_bfloat16, 64>(Q, K, V, O, c, dtype, debug_s, st);
+        return c->D == 128 ? launch_prefill<__half, 128>(Q, K, V, O, c, dtype, s, debug_s, st)
+                           : launch_prefill<__half, 64>(Q, K, V, O, c, dtype, s, debug_s, st);
+    return c->D == 128 ? launch_prefill<__nv_bfloat16, 128>(Q, K, V, O, c, dtype, s, debug_s, st)
+                       : launch_prefill<__nv_bfloat16, 64>(Q, K, V, O, c, dtype, s, debug_s, st);
 }
 
 } // namespace b200p
@@ -381,6 +414,13 @@ using namespace b200p;
 extern "C" int b200p_attn_prefill(const void* Q, const void* K, const void* V, void* O,
                                   const b200p_prefill_cfg* cfg, int dtype, b200p_stream_t stream) {
     return prefill_dispatch(Q, K, V, O, cfg, dtype, nullptr, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200p_attn_prefill_strided(const void* Q, const void* K, const void* V, void* O,
+                                          const b200p_prefill_cfg* cfg, int dtype, const b200p_attn_strides* strides,
+                                          b200p_stream_t stream) {
+    if (!strides) return B200P_E_NULL;
+    return prefill_dispatch_strided(Q, K, V, O, cfg, dtype, strides, nullptr, static_cast<cudaStream_t>(stream));
 }
 
 extern "C" int b200p_attn_prefill_debug(const void* Q, const void* K, const void* V, void* O,

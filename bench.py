@@ -444,7 +444,94 @@ class DecodeLong:
     cpu_sample_text = "8 sequences x 8192 keys (1/128 of the workload's K/V bytes)"
 
 
-WORKLOADS = {"segops": SegopsSweep, "decode": DecodeGQA, "prefill": PrefillCausal, "decode_long": DecodeLong}
+# --------------------------------------------------------------------------------------
+# workload: the small Llama-style decoder in the runtime (BASELINE config 5)
+# --------------------------------------------------------------------------------------
+class RuntimeLlama:
+    name = "runtime"
+    metric = "greedy generation throughput of the runtime (generated tokens/s; prompt 512 + 128 new tokens)"
+    unit = "tokens/s"
+    dtype = "bf16 weights and activations, fp32 hidden state and accumulation"
+    CFG = dict(n_layers=22, hidden=2048, n_heads=32, n_kv_heads=4, head_dim=64, ffn_dim=5632, vocab_size=32000, rope_theta=10000.0)
+    B, T, NEW = 2, 512, 128                    # 16 sequences over 8 GPUs = 2 per GPU
+
+    def __init__(self, n=None):
+        if n:
+            self.NEW = n
+        self.bytes_per_step = float(self.B * self.NEW)          # "units" per step = generated tokens
+        self.cases = [("generate (prefill 512 + decode)", None, None, None, self.bytes_per_step)]
+        c = self.CFG
+        qd, kvd = c["n_heads"] * c["head_dim"], c["n_kv_heads"] * c["head_dim"]
+        per_layer = (qd + 2 * kvd) * c["hidden"] + c["hidden"] * qd + 3 * c["ffn_dim"] * c["hidden"]
+        self.weight_bytes = 2 * (c["n_layers"] * per_layer + c["vocab_size"] * c["hidden"])   # read every decode step
+
+    def config(self, world):
+        return {"workload": "small Llama-style decoder in the runtime (BASELINE config 5)", **self.CFG,
+                "batch_per_gpu": self.B, "prompt_tokens": self.T, "new_tokens": self.NEW,
+                "sharding": f"sequences x{world} (2 per GPU), weights replicated, no collective",
+                "weights": "random-init bf16 ~ N(0, 0.02), norm weights 1 (no checkpoint available offline)",
+                "inputs": "uniform random token ids, seeded"}
+
+    def setup(self, torch, pkg, device, rank):
+        import numpy as np
+        self.torch, self.pkg = torch, pkg
+        c = self.CFG
+        g = torch.Generator(device=device); g.manual_seed(0xB205)        # the same model on every rank
+        H, F, D = c["hidden"], c["ffn_dim"], c["head_dim"]
+        qd, kvd = c["n_heads"] * D, c["n_kv_heads"] * D
+
+        def w(*shape):
+            return (torch.randn(shape, device=device, generator=g) * 0.02).bfloat16()
+
+        ones = torch.ones(H, device=device, dtype=torch.bfloat16)
+        layers = [{"Wq": w(qd, H), "Wk": w(kvd, H), "Wv": w(kvd, H), "Wo": w(H, qd), "Wgate": w(F, H), "Wup": w(F, H),
+                   "Wdown": w(H, F), "norm_attn": ones, "norm_mlp": ones} for _ in range(c["n_layers"])]
+        weights = {"embed_tokens": w(c["vocab_size"], H), "lm_head": w(c["vocab_size"], H), "final_norm": ones, "layers": layers}
+        self.sess = pkg.Session(c, weights, self.T + self.NEW, self.B)
+        self.ids = np.random.default_rng(0xB205 + rank).integers(0, c["vocab_size"], (self.B, self.T)).astype(np.int32)
+        self.timings = []
+        torch.cuda.synchronize()
+
+    def step(self, events=None):
+        toks, tm = self.sess.generate(self.ids, self.NEW)
+        self.timings.append(tm)
+        if events is not None:
+            e = self.torch.cuda.Event(enable_timing=True); e.record(); events.append(e)
+
+    step_e2e = step                               # generate() takes host ids and returns host tokens
+
+    def e2e_bytes(self):
+        return self.ids.nbytes, self.B * self.NEW * 4
+
+    def extra(self):
+        import statistics as st
+        tt = [t[0] for t in self.timings[-5:]]; dd = [t[1] for t in self.timings[-5:]]
+        ms_tok = st.median(dd) / max(1, self.NEW - 1)
+        kv_bytes = 2 * self.CFG["n_layers"] * self.B * self.CFG["n_kv_heads"] * (self.T + self.NEW // 2) * self.CFG["head_dim"] * 2
+        return {"ttft_ms": st.median(tt), "decode_ms_per_token": ms_tok,
+                "decode_step_bytes": self.weight_bytes + kv_bytes,
+                "decode_hbm_GBs": (self.weight_bytes + kv_bytes) / (ms_tok * 1e-3) / 1e9,
+                "gemm_calls_total": self.sess.gemm_calls}
+
+    def cpu_run(self, orc, n, threads, reps=1):
+        """n = new tokens; one sequence, prompt 64 (bounded: the CPU statement needs seconds per prompt token block)."""
+        import numpy as np
+        from oracle import runtime_ref as rr
+        if not hasattr(self, "_cpu_w"):
+            self._cpu_w = rr.make_weights(self.CFG, seed=5, kind="bf16", std=0.02)
+        ids = np.random.default_rng(1).integers(0, self.CFG["vocab_size"], (1, 64))
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            rr.RefSession(self.CFG, self._cpu_w, 64 + n, 1, "bf16").generate(ids, n)
+        dt = (time.perf_counter() - t0) / reps
+        return n / dt, dt
+
+    cpu_sample = 8
+    cpu_sample_text = "1 sequence, prompt 64 tokens + 8 new tokens (numpy restatement of the reference Session)"
+
+
+WORKLOADS = {"segops": SegopsSweep, "decode": DecodeGQA, "prefill": PrefillCausal, "decode_long": DecodeLong,
+             "runtime": RuntimeLlama}
 ALL_ORDER = ["segops", "decode", "prefill"]          # `--workload all`: the first is the headline
 
 
@@ -468,7 +555,7 @@ def cpu_line(wl, orc, steps, budget_s=120.0):
     return v, dt, len(vals), threads
 
 
-def reference_arm(args, names, rank, world):
+def reference_arm(args, names, rank, world, emit):
     """`--impl reference`: the CPU statement of the path on the host cores; rank 0 only."""
     if rank != 0:
         return
@@ -487,7 +574,7 @@ def reference_arm(args, names, rank, world):
     line = lines[0]
     if len(lines) > 1:
         line["others"] = lines[1:]
-    print(json.dumps(line), flush=True)
+    emit(line)
 
 
 def measure(wl, args, ctx):
@@ -528,7 +615,7 @@ def measure(wl, args, ctx):
     launches = pkg.launch_count() - launches0
     ms_per_step = max_over_ranks(events[0].elapsed_time(events[-1])) / args.steps
     tensor_bound = getattr(wl, "bound", "hbm") == "tensor"
-    unit_scale = 1e12 if tensor_bound else 1e9
+    unit_scale = 1e12 if tensor_bound else (1.0 if wl.unit == "tokens/s" else 1e9)
     peak = peaks["bf16_tflops"] if tensor_bound else peaks["hbm_gbs"]
     value = world * wl.bytes_per_step / (ms_per_step * 1e-3) / unit_scale
 
@@ -574,6 +661,13 @@ def measure(wl, args, ctx):
         cpu = {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
                "sample": f"{wl.cpu_sample_text}, median of {n} runs of {dt:.2f} s; independent units split over {threads} host threads"}
 
+    if hasattr(wl, "extra"):
+        ex = wl.extra()
+        roofline = {"bound": "hbm", "kernel": "decode step (weights + KV cache streamed once per token)",
+                    "achieved": round(ex["decode_hbm_GBs"], 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                    "frac": round(ex["decode_hbm_GBs"] / peaks["hbm_gbs"], 4),
+                    "peak_source": f"{peaks['source']} copy bandwidth", "traffic": None}
+        kernels = [ex]
     return {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
             "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": wl.dtype,
@@ -600,9 +694,17 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     names = ALL_ORDER if args.workload == "all" else [args.workload]
+    # stdout must carry exactly ONE JSON line: libraries that chat on file descriptor 1
+    # (NCCL prints its version there) are pointed at stderr; the line goes to the saved descriptor.
+    sys.stdout.flush()
+    real_stdout = os.dup(1)
+    os.dup2(2, 1)
+
+    def emit(obj):
+        os.write(real_stdout, (json.dumps(obj) + "\n").encode())
 
     if args.impl == "reference":
-        reference_arm(args, names, rank, world)
+        reference_arm(args, names, rank, world, emit)
         return
 
     import torch
@@ -615,7 +717,6 @@ def main():
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")      # stdout carries exactly one JSON line
         dist.init_process_group("nccl", device_id=device)
     ctx = {"torch": torch, "dist": dist, "pkg": pkg, "device": device, "rank": rank, "world": world,
            "local_rank": local_rank, "peaks": load_peaks()}
@@ -629,7 +730,7 @@ def main():
         line = lines[0]
         if len(lines) > 1:
             line["others"] = lines[1:]
-        print(json.dumps(line), flush=True)
+        emit(line)
     if world > 1:
         dist.destroy_process_group()
 

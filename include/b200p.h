@@ -122,6 +122,8 @@ typedef struct b200p_decode_args {
                                   0 = nKVHeads * stride_kv * D                            */
     long long key_offset;      /* first key of each head to attend to (a KV shard starts
                                   here); N keys are read from it                          */
+    long long q_batch_stride;  /* elements between sequences in q; 0 = nQHeads * D        */
+    long long o_batch_stride;  /* elements between sequences in o; 0 = nQHeads * D        */
 } b200p_decode_args;
 
 /* Bytes of caller-owned scratch the decode entry points need for these
@@ -195,6 +197,26 @@ typedef struct b200p_prefill_cfg {
  * B200P_E_DIM before any launch, as the reference returns hipErrorInvalidValue. */
 int b200p_attn_prefill(const void* Q, const void* K, const void* V, void* O,
                        const b200p_prefill_cfg* cfg, int dtype, b200p_stream_t stream);
+
+/* Element strides of Q, K, V and O for b200p_attn_prefill_strided: for each
+ * tensor the distance between consecutive tokens, heads and sequences (the
+ * head dimension D is always contiguous).  Every stride must be a multiple of
+ * 8 elements. */
+typedef struct b200p_attn_strides {
+    long long q_seq, q_head, q_batch;
+    long long k_seq, k_head, k_batch;
+    long long v_seq, v_head, v_batch;
+    long long o_seq, o_head, o_batch;
+} b200p_attn_strides;
+
+/* b200p_attn_prefill on tensors that are not in the dense head-major layout.
+ * It lets a runtime attend straight over token-major projections
+ * [batch, seq, heads, D] and over its KV cache [batch, nKVH, max_seq, D], which
+ * removes the four repack_kernel launches per layer and the packed K/V copies of
+ * cdna3-prims/include/cdna3/runtime/session.hpp:193-207. */
+int b200p_attn_prefill_strided(const void* Q, const void* K, const void* V, void* O,
+                               const b200p_prefill_cfg* cfg, int dtype, const b200p_attn_strides* strides,
+                               b200p_stream_t stream);
 
 /* The same launch, additionally writing the raw (unscaled) fp32 score tile
  * S = Q.K^T of the LAST 256-row query block's first 128 rows against keys

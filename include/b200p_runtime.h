@@ -1,0 +1,93 @@
+/* ---------------------------------------------------------------------------
+ * b200p_runtime.h -- C ABI of the small LLM runtime around the attention
+ * kernels: the reference's cdna3::runtime::Session
+ * (cdna3-prims/include/cdna3/runtime/session.hpp:52-331) with its KVCache
+ * (kv_cache.hpp:19-52) and the forward kernels of forward.hpp, for a batch of
+ * equal-length sequences on one GPU.
+ *
+ * Like the reference Session, a session OWNS its scratch buffers and its KV
+ * cache (allocated at creation, freed at destruction); the weights are the
+ * caller's device memory (the reference's ModelLoader role: model_loader.hpp:
+ * 134-204).  Calls on one session must come from one host thread at a time.
+ * ------------------------------------------------------------------------- */
+#ifndef B200P_RUNTIME_H_
+#define B200P_RUNTIME_H_
+
+#include "b200p.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* cdna3::runtime::ModelConfig, field for field (model_loader.hpp:51-60). */
+typedef struct b200p_model_config {
+    int n_layers;
+    int hidden;
+    int n_heads;
+    int n_kv_heads;
+    int head_dim;      /* 64 or 128 */
+    int ffn_dim;
+    int vocab_size;
+    float rope_theta;
+} b200p_model_config;
+
+/* One decoder layer's weights: 16-bit, row-major [out, in] (HF nn.Linear layout,
+ * forward.hpp:58-60).  Biases and may be NULL (Llama); norm weights are [hidden].
+ * cdna3::runtime::LayerWeights (model_loader.hpp:62-78). */
+typedef struct b200p_layer_weights {
+    const void* Wq;        /* [n_heads*head_dim, hidden]    */
+    const void* Wk;        /* [n_kv_heads*head_dim, hidden] */
+    const void* Wv;        /* [n_kv_heads*head_dim, hidden] */
+    const void* Wo;        /* [hidden, n_heads*head_dim]    */
+    const void* bq;
+    const void* bk;
+    const void* bv;
+    const void* Wgate;     /* [ffn_dim, hidden] */
+    const void* Wup;       /* [ffn_dim, hidden] */
+    const void* Wdown;     /* [hidden, ffn_dim] */
+    const void* norm_attn; /* [hidden] */
+    const void* norm_mlp;  /* [hidden] */
+} b200p_layer_weights;
+
+typedef struct b200p_model_weights {
+    b200p_model_config cfg;
+    int dtype;                          /* B200P_F16 or B200P_BF16: weights and activations */
+    const void* embed_tokens;           /* [vocab, hidden] */
+    const void* lm_head;                /* [vocab, hidden] */
+    const void* final_norm;             /* [hidden]        */
+    const b200p_layer_weights* layers;  /* host array of n_layers entries (device pointers inside) */
+} b200p_model_weights;
+
+typedef struct b200p_session b200p_session;
+
+/* Session(model, max_seq) (session.hpp:253-259) for `batch` sequences.
+ * Returns NULL and sets *status on failure. */
+b200p_session* b200p_session_create(const b200p_model_weights* weights, int max_seq, int batch, int* status);
+void b200p_session_destroy(b200p_session* s);
+
+/* Session::generate (session.hpp:263-296): greedy decoding.
+ * input_ids: host, [batch, T] token ids; out_tokens: host, [batch, max_new_tokens].
+ * Prefill of the T prompt tokens from an empty cache, then max_new_tokens - 1
+ * single-token steps.  The next-token ids stay on the device between steps (the
+ * reference copies one int to the host per token, session.hpp:329); one copy at the
+ * end returns them.  timings_ms (optional, host, 2 floats): time to first token and
+ * total decode time, measured with events on `stream`. */
+int b200p_session_generate(b200p_session* s, const int* input_ids, int T, int max_new_tokens,
+                           int* out_tokens, float* timings_ms, b200p_stream_t stream);
+
+/* Session::prefill_logits (session.hpp:299-318): prefill only; fp32 logits of the
+ * last prompt token of every sequence, host [batch, vocab]. */
+int b200p_session_prefill_logits(b200p_session* s, const int* input_ids, int T, float* logits, b200p_stream_t stream);
+
+/* One more token per sequence on top of the current cache (teacher forcing):
+ * feeds token_ids [batch] (host) at position kv_len, returns logits [batch, vocab]. */
+int b200p_session_step_logits(b200p_session* s, const int* token_ids, float* logits, b200p_stream_t stream);
+
+int b200p_session_kv_len(const b200p_session* s);
+/* Kernels of this library + cuBLAS GEMM calls issued by the session so far. */
+unsigned long long b200p_session_gemm_calls(const b200p_session* s);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200P_RUNTIME_H_ */

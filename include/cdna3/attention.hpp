@@ -57,7 +57,7 @@ inline int dtype_of(const __nv_bfloat16*) { return B200P_BF16; }
 inline b200p_decode_args args(int D, int N, int nQH, int nKVH, int stride_kv, int batch, int dtype) {
     b200p_decode_args a{};
     a.D = D; a.N = N; a.nQHeads = nQH; a.nKVHeads = nKVH; a.stride_kv = stride_kv; a.batch = batch; a.dtype = dtype;
-    a.kv_batch_stride = 0; a.key_offset = 0;
+    a.kv_batch_stride = 0; a.key_offset = 0; a.q_batch_stride = 0; a.o_batch_stride = 0;
     return a;
 }
 } // namespace detail

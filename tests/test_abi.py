@@ -10,9 +10,13 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def header_symbols():
-    text = open(os.path.join(ROOT, "include", "b200p.h")).read()
-    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
-    return sorted(set(re.findall(r"\b(b200p_[a-z0-9_]+)\s*\(", text)))
+    """Every function any include/*.h declares."""
+    import glob
+    names = set()
+    for path in glob.glob(os.path.join(ROOT, "include", "*.h")):
+        text = re.sub(r"/\*.*?\*/", "", open(path).read(), flags=re.S)
+        names |= set(re.findall(r"\b(b200p_[a-z0-9_]+)\s*\(", text))
+    return sorted(names)
 
 
 def test_header_declares_what_python_binds(b200p):

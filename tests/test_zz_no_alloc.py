@@ -18,7 +18,7 @@ def test_noalloc_decode_matches_workspace_decode(b200p, torch_cuda):
         q = torch.randn(batch, nqh, D, device="cuda", generator=g).to(dt)
         K = torch.randn(batch, nkvh, N, D, device="cuda", generator=g).to(dt)
         V = torch.randn(batch, nkvh, N, D, device="cuda", generator=g).to(dt)
-        args = b200p.DecodeArgs(D, N, nqh, nkvh, N, batch, b200p._dtype_code(q), 0, 0)
+        args = b200p.DecodeArgs(D, N, nqh, nkvh, N, batch, b200p._dtype_code(q), 0, 0, 0, 0)
         need = L.b200p_attn_decode_workspace_bytes(C.byref(args))
         assert 0 < need <= L.b200p_attn_decode_noalloc_max_bytes()
         ws = torch.empty(need, dtype=torch.uint8, device="cuda")
@@ -37,7 +37,7 @@ def test_noalloc_decode_matches_workspace_decode(b200p, torch_cuda):
             assert (o.float() - ref.float()).abs().max().item() <= 2e-2
             assert torch.equal(o, ref)
     # a shape whose partials do not fit the 8 MiB array is refused before any launch
-    big = b200p.DecodeArgs(128, 8192, 32, 8, 8192, 1024, b200p.BF16, 0, 0)
+    big = b200p.DecodeArgs(128, 8192, 32, 8, 8192, 1024, b200p.BF16, 0, 0, 0, 0)
     assert L.b200p_attn_decode_workspace_bytes(C.byref(big)) > L.b200p_attn_decode_noalloc_max_bytes()
     n0 = b200p.launch_count()
     q = torch.zeros(1, device="cuda")
