@@ -735,9 +735,22 @@ def main():
         dist.destroy_process_group()
 
 
-# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu
-# captures summarised under profiles/; filled in as captures are taken.
-TRAFFIC = {}
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
+# summarised under profiles/, scaled from the captured case to a full launch by the units
+# processed (traffic of these streaming kernels is proportional to them).
+def _seg_traffic():
+    t = {}
+    for kind, size in (("f32", 4), ("i32", 4), ("f64", 8), ("i64", 8)):
+        for op in ("sum", "max", "min"):                      # profiles/segreduce_f32_sum_2p25.md: read 1.00x, results 3x
+            t[f"reduce_{op}<{kind}>"] = (1 << 26) * size + 3 * (1 << 20) * size
+        # profiles/segscan_f64_sum_2p25.md: read 1.00x; 78 % of the output reached DRAM before the launch ended
+        t[f"scan_inclusive_sum<{kind}>"] = int((1 << 26) * size * (1.0 + 0.784))
+    return t
+
+
+TRAFFIC = _seg_traffic()
+# profiles/decode_mma_bf16_d128_n1024.md: (269.0 MB read + 4.6 MB partials) at 1024 keys -> 8192 keys
+TRAFFIC["decode_mma_kernel (+ combine)"] = int(268.98e6 * 8 + 4.55e6)
 
 if __name__ == "__main__":
     main()
