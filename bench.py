@@ -749,8 +749,9 @@ def _seg_traffic():
 
 
 TRAFFIC = _seg_traffic()
-# profiles/decode_mma_bf16_d128_n1024.md: (269.0 MB read + 4.6 MB partials) at 1024 keys -> 8192 keys
-TRAFFIC["decode_mma_kernel (+ combine)"] = int(268.98e6 * 8 + 4.55e6)
+# profiles/decode_mma_bf16_d128_n8192_full.md and profiles/prefill_tc_bf16_d128_s4096_full.md: full-size captures
+TRAFFIC["decode_mma_kernel (+ combine)"] = int(7.130e12 * 301.984e-6)
+TRAFFIC["prefill_tc_kernel"] = int(793.7e9 * 1.332064e-3)
 
 if __name__ == "__main__":
     main()
