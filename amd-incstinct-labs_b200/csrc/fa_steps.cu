@@ -105,7 +105,7 @@ fa_step_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __rest
                 dme::copy_tile_1d(Kt + nb * kBc * D, Kb + size_t(j + 1) * kBc * D, kTileBytes, &full[nb]);
                 dme::copy_tile_1d(Vt + nb * kBc * D, Vb + size_t(j + 1) * kBc * D, kTileBytes, &full[nb]);
             }
-            if (!dme::wait(&full[buf], uint32_t(j >> 1) & 1u)) { ok = false; }
+            if (!dme::wait(&full[buf], uint32_t(j >> 1) & 1u, status)) { ok = false; }
         } else {
             // cooperative synchronous tile load, 16 bytes per thread per step
             const uint4* ks = reinterpret_cast<const uint4*>(Kb + size_t(j) * kBc * D);
@@ -153,7 +153,7 @@ fa_step_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __rest
     if (STEP == 2) {
         if (!ok) atomicExch(&s_failed, 1);
         __syncthreads();
-        if (threadIdx.x == 0 && s_failed) atomicExch(status, 1);
+        if (threadIdx.x == 0 && s_failed) atomicExch(status - 1, 1);
     }
 }
 
@@ -163,6 +163,8 @@ int launch_step(const void* Q, const void* K, const void* V, void* O, int batch,
     const size_t smem = 4 * size_t(kBc) * D * sizeof(T) + (kBr * kBc + kBr * D) * sizeof(float) + 64;
     int* status = device_status_ptr();
     if (!status) return B200P_E_NO_DEVICE;
+    status += 1;                                               // per-launch abort word; [0] is the sticky report
+    if (STEP == 2) { if (cudaError_t ce = cudaMemsetAsync(status, 0, sizeof(int), st)) return int(ce); }
     auto kern = fa_step_kernel<T, D, STEP>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));

@@ -40,7 +40,9 @@
 
 namespace b200p {
 
-__device__ int g_device_status = 0;      // raised by kernels whose bounded wait gave up
+// [0]: sticky, reported by b200p_device_status; [1]: abort flag of the launch in flight (cleared by
+// every launcher on its stream), polled by the bounded waits so that one failed wait ends the launch.
+__device__ int g_device_status[2] = {0, 0};
 
 int* device_status_ptr() {
     static int* ptrs[64] = {};
@@ -58,8 +60,9 @@ namespace {
 
 constexpr int kBM = 128;                 // query rows per tile
 constexpr int kBN = 128;                 // keys per tile
-constexpr int kPrefillThreads = 384;     // 2 softmax warpgroups + a warpgroup holding the MMA and TMA warps
-constexpr int kMmaWarp = 8, kTmaWarp = 9;
+// RS = threads per query row in the softmax (1 in every instantiation).  Warps 0 .. 8*RS-1 are softmax
+// warps (tile, lane quarter), the next warpgroup holds the MMA and the TMA warp.
+constexpr int prefill_threads(int RS) { return (8 * RS + 4) * 32; }
 constexpr float kLazyRescale = 8.0f;     // log2 units
 #ifndef B200P_POLY_EVERY
 #define B200P_POLY_EVERY 0
@@ -83,6 +86,7 @@ struct PrefillParams {
     void* O;
     long long o_seq, o_head, o_batch;   // element strides of O
     float* debug_s;            // optional: raw S of tile (0,0) of CTA (0,0,0), [128][128] fp32
+    int* status;               // the library's device status word: raised by a wait that gave up, polled by all waits
     long long* timeline;       // optional (tuning aid): clock64 stamps of CTA (0,0,0), 16 slots per KV tile
     int seqQ, seqK, nQH, nKVH, group, batch, causal;
     float scale_log2;
@@ -92,8 +96,8 @@ template <typename T> struct Fmt;
 template <> struct Fmt<__half>        { static constexpr int id = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr int id = 1; };
 
-template <typename T, int D>
-__global__ void __launch_bounds__(kPrefillThreads, 1)
+template <typename T, int D, int RS>
+__global__ void __launch_bounds__(prefill_threads(RS), 1)
 prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ,
                   const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
     using Sh = PrefillShape<D>;
@@ -111,6 +115,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_failed;
 
+    constexpr int kMmaWarp = 8 * RS, kTmaWarp = 8 * RS + 1;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int nqb = (p.seqQ + 2 * kBM - 1) / (2 * kBM);
     const int qb = nqb - 1 - int(blockIdx.x);                  // heaviest (latest) query blocks first
@@ -143,10 +148,10 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     const uint32_t sm_q = dme::smem_addr(smem + Sh::OFF_Q), sm_k = dme::smem_addr(smem + Sh::OFF_K), sm_v = dme::smem_addr(smem + Sh::OFF_V);
 
     // Register budget: the softmax warpgroups hold a whole 128-column score row per thread, the
-    // MMA / TMA warpgroup needs very little; 128 * (224 + 224 + 56) = 64512 <= 65536.
+    // MMA / TMA warpgroup needs very little; the three limits must sum to no more than 3 x 168 = 504 (the launch allocation): 216 + 216 + 72.
     // (Each role branch opens with its own setmaxnreg, so the compiler sees one limit per branch.)
-    if (warp >= 8) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 56;");
+    if (warp >= 8 * RS) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 72;");
       if (warp == kTmaWarp) {
         // ---------------------------------- TMA producer ----------------------------------
         if (lane == 0) {
@@ -157,12 +162,12 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                     dme::copy_tile_4d(smem + Sh::OFF_Q + t * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapQ, sb * 64, q0[t], head, b, q_full);
             dme::Ring<KST> kr; dme::Ring<VST> vr;
             for (int j = 0; j < nmax; ++j) {
-                if (j >= KST && !dme::wait(&k_empty[kr.stage], kr.phase ^ 1u)) { atomicExch(&s_failed, 1); break; }
+                if (j >= KST && !dme::wait(&k_empty[kr.stage], kr.phase ^ 1u, p.status)) { atomicExch(&s_failed, 1); break; }
                 dme::mbar_arrive_expect_tx(&k_full[kr.stage], Sh::TILE_BYTES);
                 for (int sb = 0; sb < Sh::SUB; ++sb)
                     dme::copy_tile_4d(smem + Sh::OFF_K + kr.stage * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapK, sb * 64, j * kBN, kvh, b, &k_full[kr.stage]);
                 kr.advance();
-                if (j >= VST && !dme::wait(&v_empty[vr.stage], vr.phase ^ 1u)) { atomicExch(&s_failed, 1); break; }
+                if (j >= VST && !dme::wait(&v_empty[vr.stage], vr.phase ^ 1u, p.status)) { atomicExch(&s_failed, 1); break; }
                 dme::mbar_arrive_expect_tx(&v_full[vr.stage], Sh::TILE_BYTES);
                 for (int sb = 0; sb < Sh::SUB; ++sb)
                     dme::copy_tile_4d(smem + Sh::OFF_V + vr.stage * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapV, sb * 64, j * kBN, kvh, b, &v_full[vr.stage]);
@@ -175,15 +180,15 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             constexpr uint32_t idesc_qk = tc::instr_desc_f16(kBM, kBN, Fmt<T>::id, 0, 0);
             constexpr uint32_t idesc_pv = tc::instr_desc_f16(kBM, D, Fmt<T>::id, 0, 1);
             // Descriptors differ from a per-tile base only in the 14-bit start-address field
-            // (units of 16 bytes), so a k-step is an integer add on the base.  The k loops are kept
-            // rolled: this warp has few registers and issues 8 instructions per ~500 tensor cycles.
+            // (units of 16 bytes), so a k-step is one integer add of a compile-time constant on the base;
+            // the k loops are unrolled so that the issue overhead per MMA stays far below its 64 cycles.
             const uint64_t q_base = tc::smem_desc_sw128(sm_q, 16, 1024);
             const uint64_t k_base = tc::smem_desc_sw128(sm_k, 16, 1024);
             const uint64_t v_base = tc::smem_desc_sw128(sm_v, Sh::SUB_BYTES, 1024);
             auto issue_qk = [&](int t, int kstage) {
                 const uint64_t qd = q_base + uint64_t((t * Sh::TILE_BYTES) >> 4);
                 const uint64_t kd = k_base + uint64_t((kstage * Sh::TILE_BYTES) >> 4);
-                #pragma unroll 1
+                #pragma unroll
                 for (int ks = 0; ks < D / 16; ++ks) {
                     const uint32_t off16 = (uint32_t(ks >> 2) * Sh::SUB_BYTES + uint32_t(ks & 3) * 32u) >> 4;
                     tc::mma_ss(tmem + t * kBN, qd + off16, kd + off16, idesc_qk, ks > 0);
@@ -191,15 +196,15 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             };
             auto issue_pv = [&](int t, int vstage, bool first, int kk0) {          // half of the keys: kk0 .. kk0+3
                 const uint64_t vd = v_base + uint64_t((vstage * Sh::TILE_BYTES) >> 4);
-                #pragma unroll 1
+                #pragma unroll
                 for (int kk = kk0; kk < kk0 + kBN / 32; ++kk)
                     tc::mma_ts(tmem + 256 + t * 128, tmem + t * kBN + kk * 8, vd + uint64_t(kk * (2048 >> 4)),
                                idesc_pv, !(first && kk == 0));
             };
-            bool ok = dme::wait(q_full, 0);
+            bool ok = dme::wait(q_full, 0, p.status);
             dme::Ring<KST> kr; dme::Ring<VST> vr;
             if (ok && nmax > 0) {
-                ok = dme::wait(&k_full[kr.stage], kr.phase);
+                ok = dme::wait(&k_full[kr.stage], kr.phase, p.status);
                 tc::fence_after_sync();
                 if (ok) {
                     for (int t = 0; t < 2; ++t) if (n[t] > 0) { issue_qk(t, kr.stage); tc::commit(&s_full[t]); }
@@ -208,18 +213,18 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                 }
             }
             for (int j = 0; j < nmax && ok; ++j) {
-                ok = dme::wait(&v_full[vr.stage], vr.phase);
-                if (ok && j + 1 < nmax) ok = dme::wait(&k_full[kr.stage], kr.phase);
+                ok = dme::wait(&v_full[vr.stage], vr.phase, p.status);
+                if (ok && j + 1 < nmax) ok = dme::wait(&k_full[kr.stage], kr.phase, p.status);
                 if (!ok) break;
                 for (int t = 0; t < 2 && ok; ++t) {
                     if (j >= n[t]) continue;
-                    ok = dme::wait(&p_half[2 * t], uint32_t(j & 1));
+                    ok = dme::wait(&p_half[2 * t], uint32_t(j & 1), p.status);
                     if (!ok) break;
                     tc::fence_after_sync();
                     const bool stamp = p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 64;
                     if (stamp) p.timeline[j * 16 + 8 + 2 * t] = clock64();
                     issue_pv(t, vr.stage, j == 0, 0);                 // keys 0..63 while the softmax finishes 64..127
-                    ok = dme::wait(&p_half[2 * t + 1], uint32_t(j & 1));
+                    ok = dme::wait(&p_half[2 * t + 1], uint32_t(j & 1), p.status);
                     if (!ok) break;
                     tc::fence_after_sync();
                     issue_pv(t, vr.stage, j == 0, kBN / 32);
@@ -235,44 +240,50 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
         }
       }
     } else {
-        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;");
-        // ---------------------------------- softmax warpgroups ----------------------------
-        const int t = warp / 4;                               // query tile of this warpgroup
-        const int r = threadIdx.x % kBM;                      // row inside the tile = TMEM lane
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;");
+        // ---------------------------------- softmax warps ---------------------------------
+        // One thread owns a whole 128-key score row.  (Two threads per row, 64 keys each with a shared-memory
+        // exchange of the row maxima, was measured at 502 vs 944 TFLOP/s and is not kept.)
+        constexpr int CW = kBN / RS;                           // score columns per thread
+        constexpr int OW = D / RS;                             // output columns per thread
+        const int t = warp / (4 * RS);                        // query tile
+        const int half = (warp / 4) % RS;                     // column half of this thread
+        const int r = (warp % 4) * 32 + lane;                 // row inside the tile = TMEM lane
         const int row = q0[t] + r;
         const uint32_t lane_base = uint32_t(32 * (warp % 4)) << 16;
         const uint32_t tS = tmem + lane_base + uint32_t(t * kBN);
-        const uint32_t tO = tmem + lane_base + 256u + uint32_t(t * 128);
+        const uint32_t tO = tmem + lane_base + 256u + uint32_t(t * 128) + uint32_t(half * OW);
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n[t]; ++j) {
-            if (!dme::wait(&s_full[t], uint32_t(j & 1))) { ok = false; break; }
+            if (!dme::wait(&s_full[t], uint32_t(j & 1), p.status)) { ok = false; break; }
             tc::fence_after_sync();
-            const bool stamp = p.timeline && r == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 64;
+            const bool stamp = p.timeline && r == 0 && half == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 64;
             if (stamp) p.timeline[j * 16 + 4 * t + 0] = clock64();
             const bool need_mask = (p.causal && j * kBN + kBN - 1 > q0[t]) || (j * kBN + kBN > p.seqK);
-            const int col_limit = min(p.causal ? row : 0x7fffffff, p.seqK - 1) - j * kBN;   // columns <= col_limit are live
-            // ---- the whole score row into registers (one wait for the four loads) ------------
-            uint32_t sv[kBN];
+            // columns (of this thread's range) <= col_limit are live
+            const int col_limit = min(p.causal ? row : 0x7fffffff, p.seqK - 1) - j * kBN - half * CW;
+            // ---- this thread's part of the score row into registers (one wait for all loads) ------------
+            uint32_t sv[CW];
             #pragma unroll
-            for (int c = 0; c < kBN / 32; ++c) tc::ld_32x32b_x32(tS + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
+            for (int c = 0; c < CW / 32; ++c) tc::ld_32x32b_x32(tS + half * CW + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
             tc::wait_ld();
             if (stamp) p.timeline[j * 16 + 4 * t + 1] = clock64();
             if (p.debug_s && j == 0 && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
                 #pragma unroll
-                for (int i = 0; i < kBN; ++i) p.debug_s[r * kBN + i] = __uint_as_float(sv[i]);
+                for (int i = 0; i < CW; ++i) p.debug_s[r * kBN + half * CW + i] = __uint_as_float(sv[i]);
             }
             if (need_mask) {
                 #pragma unroll
-                for (int i = 0; i < kBN; ++i) if (i > col_limit) sv[i] = 0xff800000u;      // -inf
+                for (int i = 0; i < CW; ++i) if (i > col_limit) sv[i] = 0xff800000u;       // -inf
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // 3-input max: 64 instructions for 128 values
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // 3-input max
             #pragma unroll
-            for (int i = 0; i < kBN; i += 8) {
+            for (int i = 0; i < CW; i += 8) {
                 #pragma unroll
                 for (int u = 0; u < 4; ++u) mx4[u] = max3(mx4[u], __uint_as_float(sv[i + 2 * u]), __uint_as_float(sv[i + 2 * u + 1]));
             }
-            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+            float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             const float m_new = mx * p.scale_log2;
             float alpha = 1.f;
             if (m_new > m_used + kLazyRescale) { alpha = fast_exp2(m_used - m_new); m_used = m_new; }
@@ -280,7 +291,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             // ---- rescale O when some row of this warp moved its max (never on the first tile) ----
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
+                for (int c = 0; c < OW / 32; ++c) {
                     uint32_t v[32];
                     tc::ld_32x32b_x32(tO + c * 32, v);
                     tc::wait_ld();
@@ -290,11 +301,11 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                 }
                 tc::wait_st();
             }
-            // ---- P = exp2(S * scale - m) as 16-bit pairs over the front of S.  The first half of the keys is
-            // handed to the MMA warp as soon as it is stored; the row sum is taken after the hand-off. ----
+            // ---- P = exp2(S * scale - m) as 16-bit pairs over the front of S.  Each half of the keys is handed
+            // to the MMA warp as soon as it is stored; the row sum is taken after the hand-off. ----
             const float neg_m = -m_used;
             #pragma unroll
-            for (int c = 0; c < kBN / 32; ++c) {
+            for (int c = 0; c < CW / 32; ++c) {
                 uint32_t pk[16];
                 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
@@ -305,30 +316,31 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                     sv[c * 32 + 2 * i] = __float_as_uint(e.x); sv[c * 32 + 2 * i + 1] = __float_as_uint(e.y);
                     pk[i] = pack2<T>(e.x, e.y);
                 }
-                tc::st_32x32b_x16(tS + c * 16, pk);
-                if (c == 1 || c == 3) {
+                tc::st_32x32b_x16(tS + (half * CW) / 2 + c * 16, pk);
+                const int key_chunk = half * (CW / 32) + c;                   // 32-key chunk of the tile: 0..3
+                if (key_chunk == 1 || key_chunk == 3) {
                     tc::wait_st();
                     tc::fence_before_sync();
-                    dme::mbar_arrive(&p_half[2 * t + (c >> 1)]);
+                    dme::mbar_arrive(&p_half[2 * t + (key_chunk >> 1)]);
                 }
             }
             float la[4] = {0.f, 0.f, 0.f, 0.f};
             #pragma unroll
-            for (int i = 0; i < kBN; i += 4) {
+            for (int i = 0; i < CW; i += 4) {
                 #pragma unroll
                 for (int u = 0; u < 4; ++u) la[u] += __uint_as_float(sv[i + u]);
             }
             l = l * alpha + ((la[0] + la[1]) + (la[2] + la[3]));
             if (stamp) p.timeline[j * 16 + 4 * t + 3] = clock64();
         }
-        // ---- epilogue: O / l -> 16-bit, one row per thread -------------------------------
+        // ---- epilogue: O / l -> 16-bit; a thread writes its OW output columns of its row --------------
         if (ok && n[t] > 0) {
-            if (dme::wait(&o_done[t], 0)) {
+            if (dme::wait(&o_done[t], 0, p.status)) {
                 tc::fence_after_sync();
                 const float inv = l > 0.f ? 1.f / l : 1.f;
-                T* orow = static_cast<T*>(p.O) + size_t(b) * p.o_batch + size_t(head) * p.o_head + size_t(row) * p.o_seq;
+                T* orow = static_cast<T*>(p.O) + size_t(b) * p.o_batch + size_t(head) * p.o_head + size_t(row) * p.o_seq + half * OW;
                 #pragma unroll
-                for (int c = 0; c < D / 32; ++c) {
+                for (int c = 0; c < OW / 32; ++c) {
                     uint32_t v[32];
                     tc::ld_32x32b_x32(tO + c * 32, v);
                     tc::wait_ld();
@@ -352,11 +364,11 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     __syncthreads();
     tc::fence_after_sync();
     if (warp == kMmaWarp) tc::tmem_dealloc(tmem, 512);
-    if (threadIdx.x == 0 && s_failed) atomicExch(&g_device_status, 1);
+    if (threadIdx.x == 0 && s_failed) atomicExch(p.status - 1, 1);
 }
 
-template <typename T, int D>
-int launch_prefill(const void* Q, const void* K, const void* V, void* O, const b200p_prefill_cfg* c, int dtype,
+template <typename T, int D, int RS>
+int launch_prefill_rs(const void* Q, const void* K, const void* V, void* O, const b200p_prefill_cfg* c, int dtype,
                    const b200p_attn_strides& s, float* debug_s, cudaStream_t st) {
     using Sh = PrefillShape<D>;
     const CUtensorMapDataType dt = dtype == B200P_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
@@ -372,7 +384,7 @@ int launch_prefill(const void* Q, const void* K, const void* V, void* O, const b
     if (e == cudaSuccess) e = make_tensor_map(&mv, dt, 4, V, kd, vs, box, Swizzle::B128);
     if (e != cudaSuccess) return int(e);
 
-    auto kern = prefill_tc_kernel<T, D>;
+    auto kern = prefill_tc_kernel<T, D, RS>;
     static bool attr_set[64] = {};
     int dev = 0; cudaGetDevice(&dev);
     if (dev >= 0 && dev < 64 && !attr_set[dev]) {
@@ -382,6 +394,10 @@ int launch_prefill(const void* Q, const void* K, const void* V, void* O, const b
     }
     PrefillParams p{};
     p.O = O; p.debug_s = debug_s; p.timeline = nullptr;
+    p.status = device_status_ptr();
+    if (!p.status) return B200P_E_NO_DEVICE;
+    p.status += 1;                                              // the per-launch abort word
+    if (cudaError_t ce = cudaMemsetAsync(p.status, 0, sizeof(int), st)) return int(ce);
     if (debug_s && (tuning(KNOB_PREFILL_VARIANT, 0) & 256)) {      // tuning aid: the debug buffer receives the timeline
         p.timeline = reinterpret_cast<long long*>(debug_s); p.debug_s = nullptr;
     }
@@ -390,8 +406,14 @@ int launch_prefill(const void* Q, const void* K, const void* V, void* O, const b
     p.batch = c->batch; p.causal = c->causal;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(D));
     dim3 grid((c->seqQ + 2 * kBM - 1) / (2 * kBM), c->nQHeads, c->batch);
-    kern<<<grid, kPrefillThreads, Sh::SMEM_BYTES, st>>>(p, mq, mk, mv);
+    kern<<<grid, prefill_threads(RS), Sh::SMEM_BYTES, st>>>(p, mq, mk, mv);
     return launched();
+}
+
+template <typename T, int D>
+int launch_prefill(const void* Q, const void* K, const void* V, void* O, const b200p_prefill_cfg* c, int dtype,
+                   const b200p_attn_strides& s, float* debug_s, cudaStream_t st) {
+    return launch_prefill_rs<T, D, 1>(Q, K, V, O, c, dtype, s, debug_s, st);
 }
 
 } // namespace
@@ -462,7 +484,7 @@ extern "C" int b200p_device_status(int clear) {
     int h = 0;
     cudaError_t e = cudaDeviceSynchronize();
     if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&h, g_device_status, sizeof(int));
-    if (e == cudaSuccess && clear && h != 0) { int z = 0; e = cudaMemcpyToSymbol(g_device_status, &z, sizeof(int)); }
+    if (e == cudaSuccess && clear && h != 0) { int z[2] = {0, 0}; e = cudaMemcpyToSymbol(g_device_status, z, sizeof(z)); }
     if (e != cudaSuccess) return int(e);
     return h == 0 ? B200P_OK : B200P_E_TIMEOUT;
 }

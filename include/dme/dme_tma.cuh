@@ -61,14 +61,21 @@ __device__ __forceinline__ uint64_t global_timer_ns() {
 }
 // Bounded wait for the phase with the given parity.  false = gave up (after
 // kWaitLimitNs; the clock is read once per 256 polls).
-__device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity) {
+// `abort_flag` (optional, global memory): a word that is non-zero once ANY wait of the launch has
+// given up; every other wait then gives up at its next check instead of running out its own limit, so
+// a launch whose pipeline is broken ends within about one limit, not one limit per CTA.
+__device__ __forceinline__ bool wait(uint64_t* bar, uint32_t parity, int* abort_flag = nullptr) {
     if (mbar_try_wait(bar, parity)) return true;
     const uint64_t t0 = global_timer_ns();
     for (;;) {
         #pragma unroll 1
         for (int i = 0; i < 256; ++i)
             if (mbar_try_wait(bar, parity)) return true;
-        if (global_timer_ns() - t0 > kWaitLimitNs) return false;
+        if (abort_flag && *reinterpret_cast<volatile int*>(abort_flag) != 0) return false;
+        if (global_timer_ns() - t0 > kWaitLimitNs) {
+            if (abort_flag) atomicExch(abort_flag, 1);
+            return false;
+        }
     }
 }
 
