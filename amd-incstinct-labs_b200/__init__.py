@@ -36,6 +36,8 @@ SYMBOLS = {
     "b200p_attn_decode": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "b200p_attn_decode_partial": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _sz, _vp]),
     "b200p_attn_merge_lse": (_i, [_vp, _vp, _i, _i, _i, _ll, _ll, _i, _vp, _vp]),
+    "b200p_attn_decode_push": (_i, [_vp, _vp, _vp, _vp, _vp, _sz, _vp, _i, _vp]),
+    "b200p_attn_merge_lse_wait": (_i, [_vp, _i, _i, _i, _i, _vp, _vp, C.c_ulonglong, _vp]),
     "b200p_attn_workspace_status": (_i, [_vp, _vp]),
     "b200p_attn_decode_noalloc": (_i, [_vp, _vp, _vp, _vp, _vp, _vp]),
     "b200p_attn_decode_noalloc_max_bytes": (_sz, []),
@@ -52,6 +54,25 @@ SYMBOLS = {
     "b200p_session_gemm_calls": (C.c_ulonglong, [_vp]),
     "b200p_fa_step": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.c_float, _vp]),
 }
+
+
+MAX_PEERS = 16
+
+
+class PeerExchange(C.Structure):
+    """struct b200p_peer_exchange: every rank's receive buffer and flag array as
+    addressable from this GPU, plus this rank's local CTA counter."""
+    _fields_ = [("rank", _i), ("world", _i), ("slots", _vp * MAX_PEERS), ("flags", _vp * MAX_PEERS), ("counter", _vp)]
+
+
+def peer_exchange(rank: int, world: int, slot_ptrs, flag_ptrs, counter_ptr: int) -> PeerExchange:
+    if not (1 <= world <= MAX_PEERS) or len(slot_ptrs) != world or len(flag_ptrs) != world:
+        raise ValueError(f"world must be 1..{MAX_PEERS} with one slot and flag pointer per rank")
+    px = PeerExchange()
+    px.rank, px.world, px.counter = rank, world, counter_ptr
+    for g in range(world):
+        px.slots[g], px.flags[g] = int(slot_ptrs[g]), int(flag_ptrs[g])
+    return px
 
 
 class PrefillCfg(C.Structure):
@@ -241,6 +262,27 @@ def decode_partial(q, K, V, N=None, workspace=None, key_offset: int = 0, out=Non
     _check(lib().b200p_attn_decode_partial(q.data_ptr(), K.data_ptr(), V.data_ptr(), out.data_ptr(), lse.data_ptr(),
                                            C.byref(a), ws.data_ptr(), ws.numel(), _stream(q)), "attn_decode_partial")
     return out, lse
+
+
+def decode_push(q, K, V, px: PeerExchange, seq: int, N=None, workspace=None, key_offset: int = 0):
+    """Attention over this rank's KV shard, its (O, lse) stored into every rank's receive
+    buffer through the peer pointers of `px`, then flag word [rank] of every rank set to seq."""
+    for t, n in ((q, "q"), (K, "K"), (V, "V")):
+        _dev(t, n)
+    a, batch, nQH, D = _decode_args(q, K, N, key_offset)
+    ws = decode_workspace(q, K, N, key_offset) if workspace is None else workspace
+    _check(lib().b200p_attn_decode_push(q.data_ptr(), K.data_ptr(), V.data_ptr(), C.byref(a), ws.data_ptr(), ws.numel(),
+                                        C.byref(px), int(seq), _stream(q)), "attn_decode_push")
+
+
+def merge_lse_wait(px: PeerExchange, seq: int, rows: int, D: int, out, status, wait_ns: int = 0):
+    """Bounded wait for all ranks' flag words to reach seq, then the lse merge of this step's
+    partials from the local receive buffer into out [rows.., D].  status: int32 device tensor
+    (zeroed by the caller); 1 afterwards means a wait ran out."""
+    _dev(out, "out"); _dev(status, "status")
+    _check(lib().b200p_attn_merge_lse_wait(C.byref(px), int(seq), rows, D, _dtype_code(out), out.data_ptr(),
+                                           status.data_ptr(), int(wait_ns), _stream(out)), "attn_merge_lse_wait")
+    return out
 
 
 def merge_lse(o_parts, lse_parts, dtype, out=None):

@@ -573,6 +573,117 @@ merge_lse_kernel(const float* __restrict__ o_parts, const float* __restrict__ ls
     for (int i = 0; i < PER; ++i) o[size_t(row) * D + lane + 32 * i] = from_float<T>(acc[i] * inv);
 }
 
+// ---------------------------------------------------------------------------
+// Exchange of the (O, lse) partials over peer memory (KV sequence sharded over the
+// GPUs of one node).  Instead of writing its partial locally and handing it to a
+// collective, the combine kernel stores each normalised row straight into slot
+// [parity][rank] of EVERY rank's receive buffer (plain peer stores over NVLink, no
+// multicast), and the last CTA to finish publishes the step number in word [rank]
+// of every rank's flag array.  The merge kernel on each GPU then waits, bounded,
+// until all flag words have reached the step number and merges from its own memory.
+// Receive buffers are double-buffered by step parity: a rank can be at most one
+// step ahead of the slowest one, because its next merge needs that rank's flag.
+// ---------------------------------------------------------------------------
+struct PeerTable {
+    float* slots[B200P_MAX_PEERS];
+    int*   flags[B200P_MAX_PEERS];
+};
+
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+    int v;
+    asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+    asm volatile("st.release.sys.global.s32 [%0], %1;" :: "l"(p), "r"(v) : "memory");
+}
+
+template <int D>
+__global__ void __launch_bounds__(128)
+decode_combine_push_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits, int rows,
+                           PeerTable peers, int rank, int world, int seq, int* __restrict__ counter) {
+    const int row = blockIdx.x * 4 + threadIdx.x / 32, lane = threadIdx.x % 32;
+    constexpr int PER = D / 32;
+    if (row < rows) {
+        float M = kNegBig;
+        for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(size_t(row) * splits + s) * 2]);
+        float L = 0.f, acc[PER];
+        #pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float f = exp2f(part_ml[(size_t(row) * splits + s) * 2] - M);
+            L += f * part_ml[(size_t(row) * splits + s) * 2 + 1];
+            #pragma unroll
+            for (int i = 0; i < PER; ++i) acc[i] += f * part_o[(size_t(row) * splits + s) * D + lane + 32 * i];
+        }
+        const float inv = L > 0.f ? 1.f / L : 1.f;
+        const float lse = L > 0.f ? (M + log2f(L)) * 0.6931471805599453f : -INFINITY;
+        const size_t n = size_t(rows) * (D + 1);
+        const size_t slot = (size_t(seq & 1) * world + rank) * n;
+        for (int g = 0; g < world; ++g) {
+            float* dst = peers.slots[(rank + g) % world] + slot;         // start with the own GPU, then round the ring
+            #pragma unroll
+            for (int i = 0; i < PER; ++i) dst[size_t(row) * D + lane + 32 * i] = acc[i] * inv;
+            if (lane == 0) dst[size_t(rows) * D + row] = lse;
+        }
+    }
+    // publish: every CTA fences its stores, the last one to count in raises the flags
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const int old = atomicAdd(counter, 1);
+        if (old == int(gridDim.x) - 1) {
+            *counter = 0;                                                // ready for the next launch on this stream
+            __threadfence_system();
+            for (int g = 0; g < world; ++g) st_release_sys(peers.flags[(rank + g) % world] + rank, seq);
+        }
+    }
+}
+
+// Merge after the peer exchange: waits (bounded by wait_ns of wall time) until every
+// rank's flag word has reached `seq`, then merges the `world` packed partials of this
+// step's parity.  A wait that runs out sets *status to 1 and the launch finishes
+// without hanging (its output is then meaningless).
+template <typename T, int D>
+__global__ void __launch_bounds__(128)
+merge_lse_wait_kernel(const float* slots, const int* flags, int world, int seq, int rows,
+                      T* __restrict__ o, int* status, unsigned long long wait_ns) {
+    if (threadIdx.x < world) {
+        const int* f = flags + threadIdx.x;
+        if (ld_acquire_sys(f) < seq) {
+            const uint64_t t0 = dme::global_timer_ns();
+            for (;;) {
+                bool ok = false;
+                #pragma unroll 1
+                for (int i = 0; i < 64 && !ok; ++i) ok = ld_acquire_sys(f) >= seq;
+                if (ok) break;
+                if (*reinterpret_cast<volatile int*>(status) != 0) break;
+                if (dme::global_timer_ns() - t0 > wait_ns) { atomicExch(status, 1); break; }
+            }
+        }
+    }
+    __syncthreads();
+    const int row = blockIdx.x * 4 + threadIdx.x / 32, lane = threadIdx.x % 32;
+    if (row >= rows) return;
+    constexpr int PER = D / 32;
+    const size_t n = size_t(rows) * (D + 1);
+    const float* base = slots + size_t(seq & 1) * world * n;
+    float M = -INFINITY;
+    for (int g = 0; g < world; ++g) M = fmaxf(M, __ldcg(base + g * n + size_t(rows) * D + row));
+    float den = 0.f, acc[PER];
+    #pragma unroll
+    for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+    for (int g = 0; g < world; ++g) {
+        const float w = (M == -INFINITY) ? 0.f : __expf(__ldcg(base + g * n + size_t(rows) * D + row) - M);
+        den += w;
+        #pragma unroll
+        for (int i = 0; i < PER; ++i) acc[i] += w * __ldcg(base + g * n + size_t(row) * D + lane + 32 * i);
+    }
+    const float inv = den > 0.f ? 1.f / den : 1.f;
+    #pragma unroll
+    for (int i = 0; i < PER; ++i) o[size_t(row) * D + lane + 32 * i] = from_float<T>(acc[i] * inv);
+}
+
 // ---- host side ------------------------------------------------------------------------
 struct DecodePlan { int splits, keys_per_split; size_t ws_bytes, off_ml, off_o; };
 
@@ -677,10 +788,25 @@ int launch_combine(const float* po, const float* pml, int splits, int rows, int 
     return launched();
 }
 
+int validate_peers(const b200p_peer_exchange* px) {
+    if (!px || !px->counter) return B200P_E_NULL;
+    if (px->world < 1 || px->world > B200P_MAX_PEERS || px->rank < 0 || px->rank >= px->world) return B200P_E_RANGE;
+    for (int g = 0; g < px->world; ++g) {
+        if (!px->slots[g] || !px->flags[g]) return B200P_E_NULL;
+        if (!aligned(px->slots[g], 4) || !aligned(px->flags[g], 4)) return B200P_E_ALIGN;
+    }
+    return B200P_OK;
+}
+
 int run_decode(const b200p_decode_args* a, const void* q, const void* K, const void* V,
-               void* o, float* o_f32, float* lse, void* ws, size_t ws_bytes, cudaStream_t st) {
+               void* o, float* o_f32, float* lse, void* ws, size_t ws_bytes, cudaStream_t st,
+               const b200p_peer_exchange* px = nullptr, int seq = 0) {
     if (int e = validate(a)) return e;
-    if (!q || !K || !V || (!o && !(o_f32 && lse))) return B200P_E_NULL;
+    if (!q || !K || !V || (!px && !o && !(o_f32 && lse))) return B200P_E_NULL;
+    if (px) {
+        if (int e = validate_peers(px)) return e;
+        if (seq < 1) return B200P_E_RANGE;
+    }
     if (!aligned(K, 16) || !aligned(V, 16) || !aligned(q, 2)) return B200P_E_ALIGN;
     if (sm_count() <= 0) return B200P_E_NO_DEVICE;
     const DecodePlan pl = plan_decode(a->D, a->N, a->nQHeads, a->nKVHeads, a->batch);
@@ -713,6 +839,14 @@ int run_decode(const b200p_decode_args* a, const void* q, const void* K, const v
     if (e) return e;
     const int rows = a->batch * a->nQHeads, rps = a->nQHeads;
     const long long obs = a->o_batch_stride > 0 ? a->o_batch_stride : (long long)a->nQHeads * a->D;
+    if (px) {
+        PeerTable pt{};
+        for (int g = 0; g < px->world; ++g) { pt.slots[g] = px->slots[g]; pt.flags[g] = px->flags[g]; }
+        const int grid = (rows + 3) / 4;
+        if (a->D == 128) decode_combine_push_kernel<128><<<grid, 128, 0, st>>>(p.part_o, p.part_ml, pl.splits, rows, pt, px->rank, px->world, seq, px->counter);
+        else             decode_combine_push_kernel<64><<<grid, 128, 0, st>>>(p.part_o, p.part_ml, pl.splits, rows, pt, px->rank, px->world, seq, px->counter);
+        return launched();
+    }
     if (a->dtype == B200P_F16)
         return a->D == 128 ? launch_combine<__half, 128>(p.part_o, p.part_ml, pl.splits, rows, rps, obs, o, o_f32, lse, st)
                            : launch_combine<__half, 64>(p.part_o, p.part_ml, pl.splits, rows, rps, obs, o, o_f32, lse, st);
@@ -762,6 +896,39 @@ extern "C" int b200p_attn_merge_lse(const float* o_parts, const float* lse_parts
     } else {
         if (D == 128) merge_lse_kernel<__nv_bfloat16, 128><<<grid, 128, 0, st>>>(o_parts, lse_parts, parts, rows, os, ls, static_cast<__nv_bfloat16*>(o));
         else          merge_lse_kernel<__nv_bfloat16, 64><<<grid, 128, 0, st>>>(o_parts, lse_parts, parts, rows, os, ls, static_cast<__nv_bfloat16*>(o));
+    }
+    return launched();
+}
+
+extern "C" int b200p_attn_decode_push(const void* q, const void* K, const void* V,
+                                      const b200p_decode_args* a, void* workspace, size_t workspace_bytes,
+                                      const b200p_peer_exchange* px, int seq, b200p_stream_t stream) {
+    if (!px) return B200P_E_NULL;
+    return run_decode(a, q, K, V, nullptr, nullptr, nullptr, workspace, workspace_bytes,
+                      static_cast<cudaStream_t>(stream), px, seq);
+}
+
+extern "C" int b200p_attn_merge_lse_wait(const b200p_peer_exchange* px, int seq, int rows, int D, int dtype,
+                                         void* o, int* status, unsigned long long wait_ns, b200p_stream_t stream) {
+    if (!o || !status) return B200P_E_NULL;
+    if (int e = validate_peers(px)) return e;
+    if (dtype != B200P_F16 && dtype != B200P_BF16) return B200P_E_DTYPE;
+    if (D != 64 && D != 128) return B200P_E_DIM;
+    if (rows <= 0) return B200P_E_LENGTH;
+    if (seq < 1) return B200P_E_RANGE;
+    if (sm_count() <= 0) return B200P_E_NO_DEVICE;
+    if (wait_ns == 0) wait_ns = dme::kWaitLimitNs;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = (rows + 3) / 4;
+    const float* slots = px->slots[px->rank];
+    const int* flags = px->flags[px->rank];
+    const int w = px->world;
+    if (dtype == B200P_F16) {
+        if (D == 128) merge_lse_wait_kernel<__half, 128><<<grid, 128, 0, st>>>(slots, flags, w, seq, rows, static_cast<__half*>(o), status, wait_ns);
+        else          merge_lse_wait_kernel<__half, 64><<<grid, 128, 0, st>>>(slots, flags, w, seq, rows, static_cast<__half*>(o), status, wait_ns);
+    } else {
+        if (D == 128) merge_lse_wait_kernel<__nv_bfloat16, 128><<<grid, 128, 0, st>>>(slots, flags, w, seq, rows, static_cast<__nv_bfloat16*>(o), status, wait_ns);
+        else          merge_lse_wait_kernel<__nv_bfloat16, 64><<<grid, 128, 0, st>>>(slots, flags, w, seq, rows, static_cast<__nv_bfloat16*>(o), status, wait_ns);
     }
     return launched();
 }

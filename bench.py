@@ -374,6 +374,8 @@ class DecodeLong:
     dtype = "bf16 (fp32 softmax and accumulation)"
     scaling = "strong"
     B, NQH, NKVH, D, N = 64, 32, 8, 128, 131072
+    exchange = "auto"                     # --exchange: peer stores fused into the kernels, or NCCL all-gather
+    used_exchange = "none"
 
     def __init__(self, n=None):
         if n:
@@ -384,9 +386,12 @@ class DecodeLong:
     def config(self, world):
         return {"workload": "long-context GQA decode (BASELINE config 4, 131072-token variant)", "batch": self.B,
                 "q_heads": self.NQH, "kv_heads": self.NKVH, "head_dim": self.D, "kv_len": self.N,
-                "sharding": f"KV sequence in {world} contiguous chunks; one NCCL all-gather of (O, lse) "
-                            f"({self.B * self.NQH * (self.D + 1) * 4} B per rank) + local lse merge" if world > 1
+                "sharding": (f"KV sequence in {world} contiguous chunks; (O, lse) ({self.B * self.NQH * (self.D + 1) * 4} B per "
+                             f"rank) exchanged by " + ("peer stores from the combine kernel + flag wait in the merge kernel"
+                                                       if self.used_exchange == "peer" else "one NCCL all-gather")
+                             + ", local lse merge") if world > 1
                             else "single GPU holds the whole KV sequence; no collective",
+                "exchange": self.used_exchange,
                 "l2": "K/V shard larger than L2", "e2e": "q H2D + o D2H every step; the KV cache is resident state",
                 "inputs": "q, K, V ~ N(0,1) rounded to bf16, seeded"}
 
@@ -408,7 +413,8 @@ class DecodeLong:
             self.K[b] = torch.randn(self.K.shape[1:], device=device, generator=g).bfloat16()
             self.V[b] = torch.randn(self.K.shape[1:], device=device, generator=g).bfloat16()
         self.dec = sharding.LongContextDecoder(pkg, dist if world > 1 else None, self.B, self.NQH, self.D,
-                                               torch.bfloat16, device)
+                                               torch.bfloat16, device, exchange=self.exchange)
+        self.used_exchange = self.dec.exchange
         self.q_host = self.q.cpu().pin_memory()
         self.o_host = torch.empty(self.q.shape, dtype=torch.bfloat16).pin_memory()
         torch.cuda.synchronize()
@@ -685,6 +691,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer (end-to-end) measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
+                    help="decode_long at N>1: how the (O, lse) partials cross the GPUs")
     ap.add_argument("--elements", type=int, default=None,
                     help="problem size override (elements per dtype / kv length / seq length); "
                          "smaller cases are for profiler captures only")
@@ -723,7 +731,11 @@ def main():
     lines = []
     for name in names:
         wl = make_workload(name, args.elements)
+        if hasattr(wl, "exchange"):
+            wl.exchange = args.exchange
         lines.append(measure(wl, args, ctx))
+        if hasattr(wl, "dec"):
+            wl.dec.check()                      # a bounded wait of the peer exchange that ran out is an error
         del wl
         torch.cuda.empty_cache()
     if rank == 0:

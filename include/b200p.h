@@ -159,6 +159,44 @@ int b200p_attn_merge_lse(const float* o_parts, const float* lse_parts, int parts
                          long long o_part_stride, long long lse_part_stride,
                          int dtype, void* o, b200p_stream_t stream);
 
+/* The (O, lse) exchange fused into the kernels, over peer memory of one NVLink
+ * domain, in place of decode_partial -> all-gather -> merge_lse.  No counterpart
+ * in the reference (single GPU).
+ *
+ * Every rank owns a receive buffer of 2 * world * rows*(D+1) floats (two step
+ * parities x one packed partial per source rank: O [rows, D], then lse [rows]),
+ * an array of `world` int flag words and one local int counter, all zero before
+ * the first step.  slots[g] / flags[g] are rank g's buffer and flag array as
+ * addressable FROM THIS GPU (peer-mapped device pointers; entry [rank] is the
+ * local one).  The caller obtains them however it shares memory between its
+ * processes (CUDA IPC, symmetric memory); the library only stores through them.
+ *
+ * b200p_attn_decode_push: decode over this rank's KV shard, then store the
+ *   shard's normalised O and lse into slot [seq & 1][rank] of every rank's
+ *   buffer and, when all of it is written, store `seq` into flag word [rank] of
+ *   every rank.  `seq` starts at 1 and grows by one per step on all ranks alike.
+ * b200p_attn_merge_lse_wait: wait until all `world` local flag words are >= seq
+ *   (at most wait_ns nanoseconds of wall time, 0 = 2 s), then merge the world
+ *   partials of parity seq & 1 from the LOCAL buffer into o [rows, D].  A wait
+ *   that runs out sets *status (device int, caller-cleared) to 1 and the launch
+ *   ends; it never hangs.  Plain loads and stores only: no multicast.
+ * Each rank must run on its own GPU: a rank's merge waits for the other ranks'
+ * kernels, which is only safe when those run concurrently elsewhere. */
+#define B200P_MAX_PEERS 16
+typedef struct b200p_peer_exchange {
+    int    rank, world;
+    float* slots[B200P_MAX_PEERS];
+    int*   flags[B200P_MAX_PEERS];
+    int*   counter;
+} b200p_peer_exchange;
+
+int b200p_attn_decode_push(const void* q, const void* K, const void* V,
+                           const b200p_decode_args* args, void* workspace, size_t workspace_bytes,
+                           const b200p_peer_exchange* px, int seq, b200p_stream_t stream);
+
+int b200p_attn_merge_lse_wait(const b200p_peer_exchange* px, int seq, int rows, int D, int dtype,
+                              void* o, int* status, unsigned long long wait_ns, b200p_stream_t stream);
+
 /* Decode for callers that cannot supply scratch memory -- a serving loop whose
  * memory plan is fixed at start-up, or a host runtime that passes only its own
  * tensors and has no allocator to lend.  This entry point has no counterpart in

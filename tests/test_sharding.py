@@ -90,3 +90,13 @@ def test_long_context_protocol_on_gloo_ranks(world, tmp_path):
     for r in range(world):
         err = float(open(tmp_path / f"rank{r}.txt").read())
         assert err < 1e-5, (r, err)
+
+
+def test_exchange_layout(sharding):
+    """Receive buffer of the peer exchange: two parities of `world` packed partials, then
+    the flag words on a 256-byte boundary."""
+    for rows, D, world in [(2048, 128, 8), (24, 64, 3), (1, 128, 2)]:
+        slot_words, flag_off, total = sharding.exchange_layout(rows, D, world)
+        assert slot_words == 2 * world * rows * (D + 1)
+        assert flag_off >= slot_words and flag_off % 64 == 0 and flag_off - slot_words < 64
+        assert total >= flag_off + world and total % 64 == 0
