@@ -228,6 +228,49 @@ segscan_kernel(const S* __restrict__ in, S* __restrict__ out, size_t nvec) {
     }
 }
 
+// ---------------------------------------------------------------------------
+// Scan of 16-bit inputs, one whole segment per lane.  The fp32 Kogge-Stone order
+// the 16-bit overloads prescribe costs 47 shuffles per 32 bytes when a segment is
+// spread over four lanes, which makes that form issue-bound; a lane that holds all
+// 64 values of its segment (128 bytes, four 32-byte or eight 16-byte vectors) runs
+// the same dataflow with no cross-lane traffic.  Lanes of a warp read adjacent
+// 128-byte lines, every sector exactly once.
+// ---------------------------------------------------------------------------
+template <typename S, typename Op, int BYTES>
+__global__ void __launch_bounds__(kThreads)
+segscan_lane_kernel(const S* __restrict__ in, S* __restrict__ out, size_t nseg) {
+    using C = Codec<S>;
+    static_assert(sizeof(S) == 2, "16-bit storage");
+    constexpr int W = BYTES / 4, NV = 128 / BYTES, EPV = BYTES / 2;
+    const char* src = reinterpret_cast<const char*>(in);
+    char* dst = reinterpret_cast<char*>(out);
+    const Op op{};
+    const size_t stride = size_t(gridDim.x) * kThreads;
+    for (size_t seg = size_t(blockIdx.x) * kThreads + threadIdx.x; seg < nseg; seg += stride) {
+        uint32_t w[NV][W];
+        #pragma unroll
+        for (int j = 0; j < NV; ++j) VecIO<BYTES>::load(src + seg * 128 + size_t(j) * BYTES, w[j]);
+        float v[64];
+        #pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            float t[EPV];
+            C::unpack(w[j], t);
+            #pragma unroll
+            for (int i = 0; i < EPV; ++i) v[j * EPV + i] = t[i];
+        }
+        wave::lane_scan_kogge_stone<64>(v, op);
+        #pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            float t[EPV];
+            #pragma unroll
+            for (int i = 0; i < EPV; ++i) t[i] = v[j * EPV + i];
+            uint32_t r[W];
+            C::pack(t, r);
+            VecIO<BYTES>::store(dst + seg * 128 + size_t(j) * BYTES, r);
+        }
+    }
+}
+
 // --- single-wave probe through the public pair-per-lane API ----------------------
 template <typename T>
 __global__ void wave_probe_kernel(int fn, int op, const T* in, T* out) {
@@ -317,11 +360,33 @@ int scan_op(int op, const void* in, void* out, size_t n, cudaStream_t st) {
     }
     return B200P_E_OP;
 }
+template <typename S, typename Op>
+int launch_scan_lane(const void* in, void* out, size_t n, cudaStream_t st) {
+    const size_t nseg = n / 64;
+    const bool wide = tuning(KNOB_SEG_VEC_BYTES, 32) == 32 && aligned(in, 32) && aligned(out, 32);
+    const int grid = grid_for((nseg + 31) / 32);
+    if (wide) segscan_lane_kernel<S, Op, 32><<<grid, kThreads, 0, st>>>(static_cast<const S*>(in), static_cast<S*>(out), nseg);
+    else      segscan_lane_kernel<S, Op, 16><<<grid, kThreads, 0, st>>>(static_cast<const S*>(in), static_cast<S*>(out), nseg);
+    return launched();
+}
 template <typename S, int MODE, bool EXCL>
 int scan_bytes(int op, const void* in, void* out, size_t n, cudaStream_t st) {
     const bool wide = tuning(KNOB_SEG_VEC_BYTES, 32) == 32 && aligned(in, 32) && aligned(out, 32);
     return wide ? scan_op<S, 32, MODE, EXCL>(op, in, out, n, st) : scan_op<S, 16, MODE, EXCL>(op, in, out, n, st);
 }
+// 16-bit inclusive scans: one segment per lane (knob scan16_lane = 0 selects the
+// four-lanes-per-segment shuffle form).
+template <typename S>
+int scan_narrow(int op, const void* in, void* out, size_t n, cudaStream_t st) {
+    if (tuning(KNOB_SCAN16_LANE, 1) == 0) return scan_bytes<S, 2, false>(op, in, out, n, st);
+    switch (op) {
+        case B200P_SUM: return launch_scan_lane<S, wave::SumOp>(in, out, n, st);
+        case B200P_MAX: return launch_scan_lane<S, wave::MaxOp>(in, out, n, st);
+        case B200P_MIN: return launch_scan_lane<S, wave::MinOp>(in, out, n, st);
+    }
+    return B200P_E_OP;
+}
+
 template <typename S, bool EXCL>
 int scan_fp(int op, const void* in, void* out, size_t n, cudaStream_t st) {
     return tuning(KNOB_SCAN_FP_EXACT, 1) ? scan_bytes<S, 0, EXCL>(op, in, out, n, st)
@@ -379,8 +444,8 @@ extern "C" int b200p_segscan_inclusive(int op, int dtype, const void* in, void* 
         case B200P_F64:  return scan_fp<double, false>(op, in, out, n, st);
         case B200P_I32:  return scan_bytes<int, 1, false>(op, in, out, n, st);
         case B200P_I64:  return scan_bytes<long long, 1, false>(op, in, out, n, st);
-        case B200P_F16:  return scan_bytes<__half, 2, false>(op, in, out, n, st);
-        case B200P_BF16: return scan_bytes<__nv_bfloat16, 2, false>(op, in, out, n, st);
+        case B200P_F16:  return scan_narrow<__half>(op, in, out, n, st);
+        case B200P_BF16: return scan_narrow<__nv_bfloat16>(op, in, out, n, st);
     }
     return B200P_E_DTYPE;
 }

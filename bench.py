@@ -163,6 +163,7 @@ class SegopsSweep:
         self.torch, self.pkg = torch, pkg
         self.host = self.make_host(torch, rank)
         self.dev = {k: v.to(device, non_blocking=True) for k, v in self.host.items()}
+        self.dev_alt = {k: v.flip(0).contiguous() for k, v in self.dev.items()}     # second buffers for launch_case
         self.out = []
         for label, fn, kind, op, _ in self.cases:
             x = self.dev[kind]
@@ -187,6 +188,16 @@ class SegopsSweep:
                 e = torch.cuda.Event(enable_timing=True)
                 e.record()
                 events.append(e)
+
+    def launch_case(self, i, rep):
+        """Kernel i alone; successive reps read different input buffers (each larger than L2/2,
+        together larger than L2)."""
+        label, fn, kind, op, _ = self.cases[i]
+        x = (self.dev if rep % 2 == 0 else self.dev_alt)[kind]
+        if fn == "reduce":
+            self.pkg.segreduce(x, op, out=self.out[i])
+        else:
+            self.pkg.segscan(x, op, out=self.out[i])
 
     def step_e2e(self):
         """The same sweep through the public API from HOST buffers: H2D of every
@@ -607,41 +618,70 @@ def measure(wl, args, ctx):
         wl.step()
     barrier()
 
-    # ---- device-resident timing, one event after every launch -------------------------
-    events = []
+    # ---- device-resident timing: K steps between two events -----------------------------
     launches0 = pkg.launch_count()
     with ClockSampler(local_rank) as clk:
         barrier()
-        start = torch.cuda.Event(enable_timing=True)
-        start.record()
-        events.append(start)
+        t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0.record()
         for _ in range(args.steps):
-            wl.step(events)
+            wl.step()
+        t1.record()
         barrier()
     launches = pkg.launch_count() - launches0
-    ms_per_step = max_over_ranks(events[0].elapsed_time(events[-1])) / args.steps
+    ms_per_step = max_over_ranks(t0.elapsed_time(t1)) / args.steps
     tensor_bound = getattr(wl, "bound", "hbm") == "tensor"
     unit_scale = 1e12 if tensor_bound else (1.0 if wl.unit == "tokens/s" else 1e9)
     peak = peaks["bf16_tflops"] if tensor_bound else peaks["hbm_gbs"]
     value = world * wl.bytes_per_step / (ms_per_step * 1e-3) / unit_scale
 
-    # per-kernel durations (average over the timed steps, this rank)
+    # ---- per-kernel durations ------------------------------------------------------------
+    # (a) inside the step: the same steps again with one event after every launch (each event
+    #     costs ~3 us of stream time, and a launch is charged for write-backs its predecessor left
+    #     in L2); (b) where the workload has several kernels, each one alone: `reps` launches back
+    #     to back between two events, alternating between two input buffers so that no launch finds
+    #     its input in L2 -- the kernel's own average launch duration.
     ncase = len(wl.cases)
+    isteps = max(1, min(args.steps, 10))
+    events = [torch.cuda.Event(enable_timing=True)]
+    events[0].record()
+    for _ in range(isteps):
+        wl.step(events)
+    barrier()
     per = [0.0] * ncase
-    for s in range(args.steps):
+    for s_ in range(isteps):
         for i in range(ncase):
-            per[i] += events[s * ncase + i].elapsed_time(events[s * ncase + i + 1])
+            per[i] += events[s_ * ncase + i].elapsed_time(events[s_ * ncase + i + 1])
+    alone = None
+    if hasattr(wl, "launch_case"):
+        reps, alone = 20, []
+        for i in range(ncase):
+            for r in range(4):
+                wl.launch_case(i, r)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for r in range(reps):
+                wl.launch_case(i, r)
+            b.record()
+            b.synchronize()
+            alone.append(a.elapsed_time(b) / reps)
     kernels = []
     for i, (label, fn, kind, op, units) in enumerate(wl.cases):
         units = units / world if getattr(wl, "scaling", "weak") == "strong" else units
-        us = max(per[i] / args.steps * 1e3, 1e-3)
+        us_step = max(per[i] / isteps * 1e3, 1e-3)
+        us = max(alone[i] * 1e3, 1e-3) if alone is not None else us_step
         rate = units / (us * 1e-6) / unit_scale
-        kernels.append({"kernel": label, "us": round(us, 2), "flops" if tensor_bound else "bytes": units,
-                        wl.unit: round(rate, 1), "frac": round(rate / peak, 4)})
+        k = {"kernel": label, "us": round(us, 2), "flops" if tensor_bound else "bytes": units,
+             wl.unit: round(rate, 1), "frac": round(rate / peak, 4)}
+        if alone is not None:
+            k["us_inside_step"] = round(us_step, 2)
+        kernels.append(k)
     dom = max(range(ncase), key=lambda i: per[i])
     roofline = {"bound": "tensor" if tensor_bound else "hbm", "kernel": kernels[dom]["kernel"],
                 "achieved": kernels[dom][wl.unit], "peak": peak, "unit": wl.unit, "frac": kernels[dom]["frac"],
                 "peak_source": f"{peaks['source']} " + ("cuBLAS bf16 burst" if tensor_bound else "copy bandwidth"),
+                "timing": ("CUDA events around 20 back-to-back launches of this kernel on alternating input buffers"
+                           if alone is not None else "CUDA events around every launch of the step"),
                 "traffic": TRAFFIC.get(kernels[dom]["kernel"])}
 
     # ---- end to end: host buffers in, host results out, every step ----------------------

@@ -206,6 +206,22 @@ __device__ __forceinline__ void row_scan_kogge_stone(T (&v)[VEC], Op op, T ident
 }
 
 // ---------------------------------------------------------------------------
+// lane_scan_kogge_stone<N>: the same Kogge-Stone dataflow over N values that ONE
+// lane holds (no cross-lane traffic at all): after the step with offset o,
+// v[i] = v[i] (op) v[i - o] for i >= o.  Bitwise the result of
+// row_scan_kogge_stone over a row of N one-element lanes.  Descending i lets the
+// update run in place.
+// ---------------------------------------------------------------------------
+template <int N, typename T, typename Op>
+__device__ __forceinline__ void lane_scan_kogge_stone(T (&v)[N], Op op) {
+    #pragma unroll
+    for (int o = 1; o < N; o <<= 1) {
+        #pragma unroll
+        for (int i = N - 1; i >= o; --i) v[i] = op(v[i], v[i - o]);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // segment_scan_dpp_order<VEC>: inclusive scan of the lane's 64-element segment
 // with the reference's full-DPP association (rows of 16 + cascaded carries).
 // ---------------------------------------------------------------------------

@@ -115,21 +115,26 @@ def test_reduce_16bit_fp32_accumulation(b200p, torch_cuda, kind, vec_bytes):
         b200p.set_tuning("seg_vec_bytes", -1)
 
 
+@pytest.mark.parametrize("lane_form", [1, 0], ids=["segment-per-lane", "four-lanes"])
 @pytest.mark.parametrize("vec_bytes", [16, 32])
 @pytest.mark.parametrize("kind", ["f16", "bf16"])
 @pytest.mark.parametrize("op", ["sum", "max", "min"])
-def test_scan_16bit_bit_exact(b200p, torch_cuda, kind, op, vec_bytes):
+def test_scan_16bit_bit_exact(b200p, torch_cuda, kind, op, vec_bytes, lane_form):
+    """Both forms of the 16-bit scan (a whole segment per lane, the default, and a segment
+    spread over four lanes) give the reference's fp32 Hillis-Steele result bit for bit."""
     torch = torch_cuda
     bf = kind == "bf16"
     b200p.set_tuning("seg_vec_bytes", vec_bytes)
+    b200p.set_tuning("scan16_lane", lane_form)
     try:
-        for n in SIZES[:4]:
+        for n in SIZES:
             f = gen("f32", n, n % 1000 + 4)
             bits = orc.f32_to_bf16_bits(f) if bf else orc.f32_to_f16_bits(f)
             got = narrow_bits(torch, b200p.segscan(narrow_dev(torch, bits, kind), op))
             assert np.array_equal(got, orc.shfl_scan_narrow(orc.OPS[op], bits, bf, threads=8)), (kind, op, n)
     finally:
         b200p.set_tuning("seg_vec_bytes", -1)
+        b200p.set_tuning("scan16_lane", -1)
 
 
 def test_wave_probe_known_answers(b200p, torch_cuda):
