@@ -52,6 +52,13 @@
 #include <limits>
 #include <type_traits>
 
+// redux.sync over a sub-warp member mask is issued once per distinct mask, so for the
+// short lane groups of wide vectors a shuffle butterfly is cheaper; groups of at
+// least this many lanes use redux.sync.
+#ifndef WAVE64_REDUX_MIN_LANES
+#define WAVE64_REDUX_MIN_LANES 32
+#endif
+
 namespace wave {
 
 constexpr unsigned kFullMask = 0xffffffffu;
@@ -139,7 +146,7 @@ __device__ __forceinline__ T segment_reduce(const T (&v)[VEC], Op op) {
         for (int i = 0; i < VEC; i += 2 * s) t[i] = op(t[i + s], t[i]);
     }
     T r = t[0];
-    if constexpr (detail::has_redux<T, Op>::value) {
+    if constexpr (detail::has_redux<T, Op>::value && LPS >= WAVE64_REDUX_MIN_LANES) {
         r = detail::Redux<Op>::run(detail::segment_mask<LPS>(), r);
     } else {
         #pragma unroll
