@@ -22,6 +22,8 @@ enum Knob {
     KNOB_DECODE_SPLITS,         // split-KV count override
     KNOB_DECODE_VARIANT,        // 1: tensor-map + mma.sync kernel, 0: bulk-copy + vector kernel
     KNOB_PREFILL_VARIANT,
+    KNOB_RUNTIME_GRAPH,         // 1: the runtime replays its decode step as a CUDA graph, 0: launches it every step
+    KNOB_RUNTIME_SKINNY,        // 1: decode-step projections on skinny_gemm_kernel, 0: library GEMMs
     KNOB_SCAN16_LANE,           // 1: 16-bit scans hold a whole segment per lane, 0: four lanes per segment
     KNOB_COUNT
 };

@@ -67,7 +67,20 @@ struct DecodeParams {
     long long key_offset;         // first key of this launch inside each head (KV shards)
     long long q_batch_stride;     // elements between sequences in q
     float scale_log2;             // log2(e) / sqrt(D)
+    const int* n_dev;             // non-null: keys = min(*n_dev + n_add, N), read by the kernels (N is then the bound)
+    int n_add;
 };
+
+// Key count and keys per split of this launch.  With a device-side count the split
+// length is derived here exactly as plan_decode() derives it on the host (whole
+// 128-key tiles), over a grid sized for the bound; splits past the end are empty.
+__device__ __forceinline__ void decode_extent(const DecodeParams& p, int& N, int& per) {
+    N = p.N; per = p.keys_per_split;
+    if (p.n_dev) {
+        N = min(max(*p.n_dev + p.n_add, 0), p.N);
+        per = ((N + p.splits - 1) / p.splits + 127) / 128 * 128;
+    }
+}
 
 template <typename T> __device__ __forceinline__ void unpack8(const uint4& w, float (&f)[8]);
 template <> __device__ __forceinline__ void unpack8<__nv_bfloat16>(const uint4& w, float (&f)[8]) {
@@ -108,8 +121,10 @@ decode_splitkv_kernel(const DecodeParams p) {
 
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int k0 = min(split * p.keys_per_split, p.N);
-    const int k1 = min(k0 + p.keys_per_split, p.N);
+    int N, per;
+    decode_extent(p, N, per);
+    const int k0 = min(split * per, N);
+    const int k1 = min(k0 + per, N);
     const int ntiles = (k1 - k0 + TK - 1) / TK;
 
     const T* Kh = static_cast<const T*>(p.K) + size_t(b) * p.kv_batch_stride + size_t(kvh) * p.kv_head_stride + size_t(p.key_offset) * D;
@@ -351,8 +366,10 @@ decode_mma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK
 
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int k0 = min(split * p.keys_per_split, p.N);
-    const int k1 = min(k0 + p.keys_per_split, p.N);
+    int N, per;
+    decode_extent(p, N, per);
+    const int k0 = min(split * per, N);
+    const int k1 = min(k0 + per, N);
     const int ntiles = (k1 - k0 + TK - 1) / TK;
 
     if (threadIdx.x == 0) {
@@ -753,7 +770,9 @@ int launch_decode_d(const DecodeParams& p, int D, cudaStream_t st) {
 template <typename T, int D>
 int launch_decode_mma(const DecodeParams& p, const b200p_decode_args* a, cudaStream_t st) {
     using Sh = DecodeShape<D>;
-    // K/V as 4-D tensors (D, keys, KV heads, sequences); keys past key_offset + N read as zero
+    // K/V as 4-D tensors (D, keys, KV heads, sequences); keys past key_offset + N read as zero.
+    // With a device-side key count N is only the bound: rows between the live count and the end
+    // of the last 128-key tile are fetched as stored and masked in the softmax (their P is 0).
     CUtensorMap mk, mv;
     const uint64_t dims[4] = {uint64_t(D), uint64_t(a->key_offset + a->N), uint64_t(a->nKVHeads), uint64_t(a->batch)};
     const uint64_t strides[3] = {uint64_t(D) * 2, uint64_t(p.kv_head_stride) * 2, uint64_t(p.kv_batch_stride) * 2};
@@ -800,7 +819,7 @@ int validate_peers(const b200p_peer_exchange* px) {
 
 int run_decode(const b200p_decode_args* a, const void* q, const void* K, const void* V,
                void* o, float* o_f32, float* lse, void* ws, size_t ws_bytes, cudaStream_t st,
-               const b200p_peer_exchange* px = nullptr, int seq = 0) {
+               const b200p_peer_exchange* px = nullptr, int seq = 0, const int* n_dev = nullptr, int n_add = 0) {
     if (int e = validate(a)) return e;
     if (!q || !K || !V || (!px && !o && !(o_f32 && lse))) return B200P_E_NULL;
     if (px) {
@@ -825,6 +844,7 @@ int run_decode(const b200p_decode_args* a, const void* q, const void* K, const v
     p.q_batch_stride = a->q_batch_stride > 0 ? a->q_batch_stride : (long long)a->nQHeads * a->D;
     if (p.q_batch_stride % 2) return B200P_E_ALIGN;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(a->D));
+    p.n_dev = n_dev; p.n_add = n_add;
     // K/V rows must start on 16 bytes for the bulk copies
     if ((p.kv_head_stride * 2) % 16 || (p.kv_batch_stride * 2) % 16) return B200P_E_ALIGN;
 
@@ -869,6 +889,14 @@ extern "C" int b200p_attn_decode(const void* q, const void* K, const void* V, vo
                                  b200p_stream_t stream) {
     if (!o) return B200P_E_NULL;
     return run_decode(a, q, K, V, o, nullptr, nullptr, workspace, workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200p_attn_decode_dyn(const void* q, const void* K, const void* V, void* o,
+                                     const b200p_decode_args* a, const int* n_dev, int n_add,
+                                     void* workspace, size_t workspace_bytes, b200p_stream_t stream) {
+    if (!o || !n_dev) return B200P_E_NULL;
+    return run_decode(a, q, K, V, o, nullptr, nullptr, workspace, workspace_bytes, static_cast<cudaStream_t>(stream),
+                      nullptr, 0, n_dev, n_add);
 }
 
 extern "C" int b200p_attn_decode_partial(const void* q, const void* K, const void* V, float* o_f32, float* lse,

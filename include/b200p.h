@@ -139,6 +139,18 @@ int b200p_attn_decode(const void* q, const void* K, const void* V, void* o,
                       const b200p_decode_args* args, void* workspace, size_t workspace_bytes,
                       b200p_stream_t stream);
 
+/* b200p_attn_decode with the key count read on the device: the kernels attend to
+ * min(*n_dev + n_add, args->N) keys, where args->N is now only an upper bound that
+ * sizes the grid, the split plan and the workspace.  The launch parameters then do
+ * not change from step to step, so a decode step can be captured once in a CUDA
+ * graph and replayed while a device-side counter advances (the reference passes N
+ * by value, attention.hpp:117-137, and re-launches every step).  K and V rows
+ * between the live count and the next multiple of 128 (inside args->N) are fetched
+ * and multiplied by a zero probability: they must hold finite values. */
+int b200p_attn_decode_dyn(const void* q, const void* K, const void* V, void* o,
+                          const b200p_decode_args* args, const int* n_dev, int n_add,
+                          void* workspace, size_t workspace_bytes, b200p_stream_t stream);
+
 /* The same attention over a shard of the KV sequence, returning what the
  * cross-shard combine needs: o_f32 [batch, nQH, D] normalised over the shard and
  * lse [batch, nQH] (natural log of the shard's softmax denominator, including

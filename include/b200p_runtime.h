@@ -83,9 +83,26 @@ int b200p_session_prefill_logits(b200p_session* s, const int* input_ids, int T, 
  * feeds token_ids [batch] (host) at position kv_len, returns logits [batch, vocab]. */
 int b200p_session_step_logits(b200p_session* s, const int* token_ids, float* logits, b200p_stream_t stream);
 
+/* The decode step's projection kernel on its own: Y[M, N] = X[M, K] . W[N, K]^T for M <= 8,
+ * 16-bit operands, fp32 accumulation.  Stands in for the rocBLAS calls of the decode step
+ * (rocblas_gemm.hpp:112-209) together with the kernels around them:
+ *   prologue 0: X = x16 [M, ldx] (16-bit);
+ *   prologue 1: X = RMSNorm(x32 [M, K] fp32) * norm_w, rounded to 16 bits (forward.hpp:34-56);
+ *   epilogue 0: out 16-bit [M, ldo];  2: out fp32;  1: out fp32 += Y (residual);
+ *   epilogue 3: W is [2N, K] (gate rows, then up rows), out 16-bit = SiLU(gate) * up
+ *               (forward.hpp:154-160).
+ * Combinations: prologue 1 with epilogues 0, 2, 3; prologue 0 with epilogue 1.
+ * K must be a multiple of 16; B200P_E_RANGE for shapes outside the kernel's domain. */
+int b200p_skinny_gemm(int dtype, int prologue, int epilogue, const void* W, const void* x16, const float* x32,
+                      const void* norm_w, void* out, int M, int N, int K, int ldx, int ldo, float eps,
+                      b200p_stream_t stream);
+
 int b200p_session_kv_len(const b200p_session* s);
 /* Kernels of this library + cuBLAS GEMM calls issued by the session so far. */
 unsigned long long b200p_session_gemm_calls(const b200p_session* s);
+/* Decode steps of b200p_session_generate that ran as replays of the captured step graph
+ * (every step after the first of a call, unless b200p_set_tuning("runtime_graph", 0)). */
+unsigned long long b200p_session_graph_replays(const b200p_session* s);
 
 #ifdef __cplusplus
 }

@@ -166,3 +166,51 @@ def test_full_size_config_sampled(b200p, torch_cuda):
     merged = b200p.merge_lse(torch.stack([p[0] for p in parts]), torch.stack([p[1] for p in parts]), torch.bfloat16)
     assert (merged.float() - got.float()).abs().max().item() < 1e-2
     assert torch.equal(b200p.decode(q, K, V, workspace=ws), got)       # run-to-run identical
+
+
+@pytest.mark.parametrize("D,nqh,nkvh", [(128, 8, 2), (64, 32, 4)])
+def test_device_side_key_count(b200p, torch_cuda, D, nqh, nkvh):
+    """decode_dyn reads the key count on the device: for every count it equals the oracle and
+    the by-value launch over the same strided cache; rows past the count are finite filler."""
+    torch = torch_cuda
+    rng = np.random.default_rng(77)
+    cap, batch = 1024, 2
+    q = dev16(torch, rng.standard_normal((batch, nqh, D)).astype(np.float32), "bf16")
+    K = dev16(torch, rng.standard_normal((batch, nkvh, cap, D)).astype(np.float32), "bf16")
+    V = dev16(torch, rng.standard_normal((batch, nkvh, cap, D)).astype(np.float32), "bf16")
+    n_dev = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ws = b200p.decode_workspace(q, K)
+    for n in (1, 2, 127, 128, 129, 500, 1023, 1024, 5000):
+        n_dev.fill_(n - 1)
+        got = b200p.decode_dyn(q, K, V, n_dev, n_add=1, workspace=ws)
+        live = min(n, cap)                                              # counts past the bound are clamped
+        ref = orc.cpu_decode(q.float().cpu().numpy(), K.float().cpu().numpy(), V.float().cpu().numpy(), D, live, nqh, nkvh,
+                             stride_kv=cap, batch=batch, threads=8)
+        assert np.abs(got.float().cpu().numpy() - ref).max() < TOL, n
+        assert (got.float() - b200p.decode(q, K, V, N=live).float()).abs().max().item() < 1e-2, n
+
+
+def test_device_side_key_count_in_a_graph(b200p, torch_cuda):
+    """One captured launch, replayed while the device-side count advances."""
+    torch = torch_cuda
+    rng = np.random.default_rng(78)
+    D, nqh, nkvh, cap, batch = 128, 8, 2, 512, 2
+    q = dev16(torch, rng.standard_normal((batch, nqh, D)).astype(np.float32), "bf16")
+    K = dev16(torch, rng.standard_normal((batch, nkvh, cap, D)).astype(np.float32), "bf16")
+    V = dev16(torch, rng.standard_normal((batch, nkvh, cap, D)).astype(np.float32), "bf16")
+    n_dev = torch.full((1,), 3, dtype=torch.int32, device="cuda")
+    ws = b200p.decode_workspace(q, K)
+    out = torch.empty_like(q)
+    stream = torch.cuda.Stream()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(stream):
+        b200p.decode_dyn(q, K, V, n_dev, workspace=ws, out=out)          # warm-up outside the capture
+        torch.cuda.synchronize()
+        with torch.cuda.graph(graph, stream=stream):
+            b200p.decode_dyn(q, K, V, n_dev, workspace=ws, out=out)
+            n_dev.add_(1)
+    for n in range(3, 3 + 6):
+        graph.replay()
+        torch.cuda.synchronize()
+        assert (out.float() - b200p.decode(q, K, V, N=n).float()).abs().max().item() < 1e-2, n
+    assert int(n_dev.item()) == 9

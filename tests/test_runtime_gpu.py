@@ -89,6 +89,39 @@ def test_generate_equals_stepwise_greedy(b200p, torch_cuda):
     sess.close()
 
 
+def test_generate_graph_replay_equals_launched_steps(b200p, torch_cuda):
+    """From its second decode step on, generate() replays one captured CUDA graph whose kernels
+    read position and output column on the device.  Same tokens as with the graph switched off,
+    as the host-driven loop, across calls with a different prompt length and token budget."""
+    torch = torch_cuda
+    cfg, kind, batch, max_seq = SMALL, "bf16", 2, 1024
+    w = rr.make_weights(cfg, seed=4, kind=kind, std=0.05)
+    sess = b200p.Session(cfg, to_device(torch, w, kind), max_seq, batch)
+    rng = np.random.default_rng(10)
+    for T, new in ((300, 10), (37, 16), (300, 10)):
+        ids = rng.integers(0, cfg["vocab_size"], (batch, T)).astype(np.int32)
+        before = sess.graph_replays
+        toks, _ = sess.generate(ids, new)
+        assert sess.graph_replays - before == new - 2
+        assert sess.kv_len == T + new - 1
+        b200p.set_tuning("runtime_graph", 0)
+        try:
+            before = sess.graph_replays
+            plain, _ = sess.generate(ids, new)
+            assert sess.graph_replays == before
+        finally:
+            b200p.set_tuning("runtime_graph", -1)
+        assert np.array_equal(toks, plain)
+        lg = sess.prefill_logits(ids)
+        for s_ in range(new):
+            nxt = np.argmax(orc.round_to(lg, kind), axis=-1).astype(np.int32)
+            assert np.array_equal(toks[:, s_], nxt), s_
+            if s_ + 1 < new:
+                lg = sess.step_logits(nxt)
+    assert b200p.device_status() == 0
+    sess.close()
+
+
 def test_session_argument_errors(b200p, torch_cuda):
     torch = torch_cuda
     cfg = dict(SMALL, head_dim=96)
