@@ -23,6 +23,7 @@ enum Knob {
     KNOB_DECODE_VARIANT,        // 1: tensor-map + mma.sync kernel, 0: bulk-copy + vector kernel
     KNOB_PREFILL_VARIANT,
     KNOB_RUNTIME_GRAPH,         // 1: the runtime replays its decode step as a CUDA graph, 0: launches it every step
+    KNOB_RUNTIME_PDL,           // 1: skinny kernels launch as programmatic dependents (weights prefetched before the wait)
     KNOB_RUNTIME_SKINNY,        // 1: decode-step projections on skinny_gemm_kernel, 0: library GEMMs
     KNOB_SCAN16_LANE,           // 1: 16-bit scans hold a whole segment per lane, 0: four lanes per segment
     KNOB_COUNT
@@ -40,5 +41,14 @@ inline int launched(unsigned n = 1) {
     cudaError_t e = cudaGetLastError();
     return e == cudaSuccess ? B200P_OK : int(e);
 }
+
+// Programmatic dependent launch (PTX griddepcontrol).  launch_dependents: the next kernel in
+// the stream, if it was launched as a programmatic dependent, may start once every CTA of this
+// grid has passed this point or exited.  wait: blocks until all predecessor grids have
+// completed and their writes are visible; returns at once in a normally launched kernel.
+#ifdef __CUDACC__
+__device__ __forceinline__ void griddep_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void griddep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#endif
 
 } // namespace b200p

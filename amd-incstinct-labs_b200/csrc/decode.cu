@@ -121,6 +121,7 @@ decode_splitkv_kernel(const DecodeParams p) {
 
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    griddep_launch_dependents();                  // a programmatic dependent may begin its own prefetch
     int N, per;
     decode_extent(p, N, per);
     const int k0 = min(split * per, N);
@@ -366,6 +367,7 @@ decode_mma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK
 
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    griddep_launch_dependents();                  // a programmatic dependent may begin its own prefetch
     int N, per;
     decode_extent(p, N, per);
     const int k0 = min(split * per, N);
@@ -540,6 +542,7 @@ __global__ void __launch_bounds__(128)
 decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml, int splits, int rows,
                       int rows_per_seq, long long o_batch_stride,
                       T* __restrict__ o, float* __restrict__ o_f32, float* __restrict__ lse) {
+    griddep_launch_dependents();
     const int row = blockIdx.x * 4 + threadIdx.x / 32, lane = threadIdx.x % 32;
     if (row >= rows) return;
     constexpr int PER = D / 32;

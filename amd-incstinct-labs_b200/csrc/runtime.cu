@@ -41,6 +41,7 @@ namespace {
 // forward.hpp:174-183: out[t, :] = float(embed[ids[t], :])
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ embed, const int* __restrict__ ids, float* __restrict__ out, int M, int H) {
+    griddep_launch_dependents();
     const int t = blockIdx.x;
     if (t >= M) return;
     const T* src = embed + size_t(ids[t]) * H;
@@ -83,6 +84,7 @@ __global__ void rope_scatter_kernel(T* __restrict__ qkv, const T* __restrict__ b
                                     const float* __restrict__ sin_t, T* __restrict__ kcache, T* __restrict__ vcache,
                                     int B, int Tn, int nQH, int nKVH, int D, int pos0, int max_seq,
                                     const int* __restrict__ pos_dev) {
+    griddep_launch_dependents();
     if (pos_dev) pos0 = min(*pos_dev, max_seq - Tn);         // device-side position (graph replay), kept inside the cache
     const int half = D / 2;
     const int slots = nQH + 2 * nKVH;                       // q heads, k heads, v heads
@@ -130,15 +132,23 @@ __global__ void silu_mul_cast_kernel(const float* __restrict__ gu, T* __restrict
 }
 
 // forward.hpp:244-262 argmax over a [V] row of 16-bit logits; ties go to the lowest index.
-// One block per sequence; writes the id for the next step and the output token.
+// The row is spread over gridDim.y blocks: each folds its slice into a 64-bit key
+// (order-preserving value bits, then the complemented index) and merges it into keys[row] with
+// atomicMax; the last block of a row to arrive (ticket counter) writes the id for the next
+// step and the output token, and clears key and counter for the next launch.
 template <typename T>
 __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __restrict__ next_ids,
-                              int* __restrict__ tokens, int tokens_stride, int step, const int* __restrict__ step_dev) {
+                              int* __restrict__ tokens, int tokens_stride, int step, const int* __restrict__ step_dev,
+                              unsigned long long* __restrict__ keys, unsigned int* __restrict__ tickets) {
+    griddep_launch_dependents();
     if (step_dev) step = min(*step_dev, tokens_stride - 1);
     __shared__ unsigned long long red[32];
-    const float* row = logits + size_t(blockIdx.x) * V;
+    const int rowi = blockIdx.x;
+    const float* row = logits + size_t(rowi) * V;
+    const int per = (V + gridDim.y - 1) / gridDim.y;
+    const int i0 = blockIdx.y * per, i1 = min(i0 + per, V);
     unsigned long long best = 0;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = i0 + threadIdx.x; i < i1; i += blockDim.x) {
         const float v = to_float(from_float<T>(row[i]));                 // the reference's logits are 16-bit
         unsigned u = __float_as_uint(v);
         u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);                  // order-preserving key
@@ -153,9 +163,16 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int V, int* __re
         unsigned long long t = lane < nw ? red[lane] : 0ull;
         t = wave::dpp::reduce_max(t);
         if (lane == 0) {
-            const int id = int(0xffffffffu - unsigned(t & 0xffffffffu));
-            next_ids[blockIdx.x] = id;
-            if (tokens) tokens[size_t(blockIdx.x) * tokens_stride + step] = id;
+            atomicMax(&keys[rowi], t);
+            __threadfence();
+            if (atomicAdd(&tickets[rowi], 1u) == gridDim.y - 1) {        // every slice of the row is in
+                __threadfence();
+                const unsigned long long k = atomicExch(&keys[rowi], 0ull);
+                tickets[rowi] = 0u;
+                const int id = int(0xffffffffu - unsigned(k & 0xffffffffu));
+                next_ids[rowi] = id;
+                if (tokens) tokens[size_t(rowi) * tokens_stride + step] = id;
+            }
         }
     }
 }
@@ -173,6 +190,9 @@ __global__ void concat_rows_kernel(T* __restrict__ dst, const T* __restrict__ a,
 // decoded (= keys already in the cache), state[1] = column of the output it produces.
 __global__ void set_state_kernel(int* state, int pos, int step) { state[0] = pos; state[1] = step; }
 __global__ void advance_state_kernel(int* state) { state[0] += 1; state[1] += 1; }
+
+// argmax: rows x slices of ~2048 logits
+inline dim3 argmax_grid(int rows, int V) { return dim3(unsigned(rows), unsigned((V + 2047) / 2048), 1); }
 
 inline unsigned blocks(size_t n, int tpb = 256) { return unsigned((n + tpb - 1) / tpb); }
 
@@ -194,6 +214,8 @@ struct b200p_session {
     void *kcache = nullptr, *vcache = nullptr, *decode_ws = nullptr;
     size_t decode_ws_bytes = 0;
     int *d_ids = nullptr, *d_next = nullptr, *d_tokens = nullptr, *d_state = nullptr;
+    unsigned long long* d_keys = nullptr;                // argmax merge keys [batch], zero between launches
+    unsigned int* d_tickets = nullptr;                   // argmax arrival counters [batch]
     void* blas_ws = nullptr;
     static constexpr size_t kBlasWsBytes = size_t(64) << 20;
     // one decode step (embed -> layers -> logits -> argmax -> advance) as an executable graph
@@ -409,7 +431,7 @@ int decode_step_device_state(b200p_session* s, int max_new, cudaStream_t st) {
     launched();
     if (int e = run_layers<T>(s, 1, 0, st, s->d_state)) return e;
     if (int e = skinny_ok(s, B) ? last_logits_skinny<T>(s, st) : last_logits<T>(s, 1, st)) return e;
-    argmax_kernel<T><<<B, 256, 0, st>>>(s->logits, V, s->d_next, s->d_tokens, max_new, 0, s->d_state + 1);
+    argmax_kernel<T><<<argmax_grid(B, V), 256, 0, st>>>(s->logits, V, s->d_next, s->d_tokens, max_new, 0, s->d_state + 1, s->d_keys, s->d_tickets);
     advance_state_kernel<<<1, 1, 0, st>>>(s->d_state);
     return launched(2);
 }
@@ -467,7 +489,7 @@ int generate(b200p_session* s, const int* ids, int Tn, int max_new, int* out, fl
         if ((rc = run_layers<T>(s, Tn, 0, st))) break;
         s->kv_len = Tn;
         if ((rc = last_logits<T>(s, Tn, st))) break;
-        argmax_kernel<T><<<B, 256, 0, st>>>(s->logits, V, s->d_next, s->d_tokens, max_new, 0, nullptr);
+        argmax_kernel<T><<<argmax_grid(B, V), 256, 0, st>>>(s->logits, V, s->d_next, s->d_tokens, max_new, 0, nullptr, s->d_keys, s->d_tickets);
         set_state_kernel<<<1, 1, 0, st>>>(s->d_state, Tn, 1);
         launched(2);
         cudaEventRecord(e1, st);
@@ -575,6 +597,10 @@ int build(b200p_session* s, const b200p_model_weights* w) {
     if ((e = s->alloc(&s->last_norm, size_t(s->batch) * H * 2))) return int(e);
     if ((e = s->alloc(&s->d_next, size_t(s->batch) * sizeof(int)))) return int(e);
     if ((e = s->alloc(&s->d_state, 2 * sizeof(int)))) return int(e);
+    if ((e = s->alloc(&s->d_keys, size_t(s->batch) * sizeof(unsigned long long)))) return int(e);
+    if ((e = s->alloc(&s->d_tickets, size_t(s->batch) * sizeof(unsigned int)))) return int(e);
+    if ((e = cudaMemset(s->d_keys, 0, size_t(s->batch) * sizeof(unsigned long long)))) return int(e);
+    if ((e = cudaMemset(s->d_tickets, 0, size_t(s->batch) * sizeof(unsigned int)))) return int(e);
     if ((e = s->alloc(&s->blas_ws, b200p_session::kBlasWsBytes))) return int(e);
     // decode scratch for the longest cache
     b200p_decode_args a{};

@@ -5,21 +5,32 @@
 // M = batch (cdna3-prims/include/cdna3/runtime/rocblas_gemm.hpp:112-209) between
 // separate RMSNorm / SiLU kernels (forward.hpp:34-56, 154-160).  With a handful of
 // rows these products are streams over the weight matrix: HBM-bound, and short
-// enough that launch and dependency latency count.  This kernel treats them so:
+// enough that launch and dependency latency count.  This kernel treats them so.
 //
-//  * W is [N, K] with K contiguous, so one warp owns two output columns (two rows
-//    of W) and streams them with 32-byte loads, 4 x 2 vectors in flight per lane,
-//    issued BEFORE the prologue so that weights travel while activations are
-//    prepared; nothing of W is ever staged in shared memory;
-//  * X (16-bit, at most 8 rows) sits in shared memory, read as 32-byte rows;
-//    accumulation is fp32, the lanes' partial sums meet in the warp butterfly of
-//    wave64.cuh (wave::dpp::reduce_sum, 32-lane form);
-//  * prologue PRO_RMSNORM computes the RMSNorm of the fp32 residual stream (one
-//    warp per row) straight into shared memory: the norm kernel and its 16-bit
-//    round trip through HBM are gone;
-//  * epilogues: 16-bit store (Q/K/V), fp32 store (logits), fp32 accumulate into
-//    the residual stream (O and down projections: the GEMM's beta = 1), and
-//    SiLU(gate) * up over row pairs (n, n + F) of the concatenated gate/up matrix.
+//  * One CTA owns 16 rows of W (16 output columns); its 8 warps split K.  Every
+//    lane loads 32 contiguous bytes of one row per step, four steps for each of
+//    its two rows in flight (the whole share of a warp when K = 2048), issued
+//    BEFORE the prologue so that the weights travel while the activations are
+//    prepared.  W never touches shared memory.
+//  * The product runs on the tensor cores as mma.sync m16n8k16 with W as the A
+//    operand (16 rows) and X^T as B (8 columns = up to 8 rows of X).  A dot
+//    product does not care about the order of k, so the 16 values a lane loaded
+//    ARE its A fragments: within a 64-wide block, lane t4 of a row's four lanes
+//    supplies columns 16*t4 + 4s .. +3 to k-step s, and reads the same columns
+//    of X for the B fragment.  No unpacking, no shuffles: 4 MMAs per 2 KB of W.
+//  * X (16-bit, M rounded up to 1, 2, 4 or 8 rows) sits in shared memory with rows 16 bytes
+//    longer than K, which makes the 16-byte fragment reads bank-conflict free.
+//  * Prologue PRO_RMSNORM computes the RMSNorm of the fp32 residual stream
+//    straight into shared memory (all 8 warps, values held in registers between
+//    the sum of squares and the scaling): the norm kernel and its 16-bit round
+//    trip through HBM are gone.
+//  * The kernel is launched as a programmatic dependent of its predecessor: its
+//    CTAs start while that kernel drains, put their weight loads in flight, and
+//    only then wait (griddepcontrol.wait) for the activations.
+//  * The 8 partial accumulators meet in shared memory; epilogues: 16-bit store
+//    (Q/K/V), fp32 store (logits), fp32 accumulate into the residual stream (O
+//    and down projections: the GEMM's beta = 1), and SiLU(gate) * up, for which a
+//    CTA takes 8 gate rows and the 8 matching up rows of the concatenated matrix.
 //
 // Same arithmetic contract as the GEMM path: 16-bit operands, fp32 products and
 // sums, outputs rounded once.
@@ -27,6 +38,7 @@
 #pragma once
 #include "common.cuh"
 #include "attn_common.cuh"
+#include "mma_sync.cuh"
 #include "vec_io.cuh"
 #include "wave_primitives/wave64.cuh"
 #include <cuda_bf16.h>
@@ -48,184 +60,214 @@ struct SkinnyArgs {
 };
 
 constexpr int kSkinnyThreads = 256;
+constexpr int kSkinnyWarps = kSkinnyThreads / 32;
 constexpr int kSkinnyMaxM = 8;
-constexpr int kSkinnyChunks = 4;      // 32-byte vectors per lane per row in flight
+constexpr int kSkinnyDepth = 4;       // 64-column blocks in flight per warp
+constexpr int kSkinnyXPad = 8;        // elements: X rows are 16 bytes longer than K
 
-template <typename T> __device__ __forceinline__ void unpack_pair(uint32_t w, float& a, float& b);
-template <> __device__ __forceinline__ void unpack_pair<__nv_bfloat16>(uint32_t w, float& a, float& b) {
-    a = __uint_as_float(w << 16); b = __uint_as_float(w & 0xffff0000u);
-}
-template <> __device__ __forceinline__ void unpack_pair<__half>(uint32_t w, float& a, float& b) {
-    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
-    a = f.x; b = f.y;
-}
-
-template <typename T, int MT, int PRO, int EPI>
+template <typename T, int PRO, int EPI>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
 skinny_gemm_kernel(const SkinnyArgs a) {
-    extern __shared__ __align__(32) unsigned char skinny_smem[];
-    T* xs = reinterpret_cast<T*>(skinny_smem);                 // [MT][K]
-    constexpr int CH = kSkinnyChunks;
+    griddep_launch_dependents();
+    extern __shared__ __align__(16) unsigned char skinny_smem[];
+    T* xs = reinterpret_cast<T*>(skinny_smem);                 // [Mp][K + pad]
+    __shared__ float red[kSkinnyWarps][32][4];
+    __shared__ float part_ss[kSkinnyWarps];
+    constexpr int DEPTH = kSkinnyDepth;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
-    const int K = a.K;
-    const int nchunk = (K + 511) / 512;                        // 512 elements = 32 lanes x 16
-    const int npairs = EPI == EPI_SILU16 ? a.N : (a.N + 1) / 2;
-    const int nwarps = gridDim.x * (kSkinnyThreads / 32);
-    const char* Wb = static_cast<const char*>(a.W);
+    const int g = lane / 4, t4 = lane % 4;
+    const int K = a.K, xstride = K + kSkinnyXPad;
+    const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;   // rows of X kept in shared memory
 
-    uint32_t wreg[2][CH][8];
-    // rows of W for pair p, and whether the second exists
-    auto rows_of = [&](int p, size_t& r0, size_t& r1, bool& has1) {
-        if (EPI == EPI_SILU16) { r0 = size_t(p); r1 = size_t(p) + size_t(a.N); has1 = true; }
-        else                   { r0 = 2 * size_t(p); r1 = r0 + 1; has1 = int(r1) < a.N; }
-    };
-    auto load_group = [&](int p, int c0) {
-        size_t r0, r1; bool has1;
-        rows_of(p, r0, r1, has1);
-        #pragma unroll
-        for (int c = 0; c < CH; ++c) {
-            const int k0 = ((c0 + c) * 32 + lane) * 16;
-            if (c0 + c < nchunk && k0 < K) {
-                VecIO<32>::load(Wb + (r0 * K + k0) * 2, wreg[0][c]);
-                if (has1) VecIO<32>::load(Wb + (r1 * K + k0) * 2, wreg[1][c]);
+    // the CTA's rows: half 0 -> accumulator rows g, half 1 -> rows g + 8
+    size_t rowA, rowB;
+    if (EPI == EPI_SILU16) {
+        const int p = min(blockIdx.x * 8 + g, a.N - 1);        // pair index: gate row p, up row N + p
+        rowA = size_t(p); rowB = size_t(a.N) + size_t(p);
+    } else {
+        rowA = size_t(min(blockIdx.x * 16 + g, a.N - 1));
+        rowB = size_t(min(blockIdx.x * 16 + g + 8, a.N - 1));
+    }
+    const char* wA = static_cast<const char*>(a.W) + rowA * size_t(K) * 2;
+    const char* wB = static_cast<const char*>(a.W) + rowB * size_t(K) * 2;
+
+    // this warp's share of K, in blocks of 64 columns
+    const int nblk = (K + 63) / 64;
+    const int per = (nblk + kSkinnyWarps - 1) / kSkinnyWarps;
+    const int b0 = warp * per, b1 = min(b0 + per, nblk);
+
+    uint32_t wb[DEPTH][2][8];
+    // A block is taken by the whole warp or not at all (mma.sync needs every lane); a lane whose 16
+    // columns lie past K (K not a multiple of 64) contributes zeros instead of loading.
+    auto lane_live = [&](int blk) { return blk * 64 + t4 * 16 < K; };
+    auto issue = [&](int slot, int blk) {
+        if (blk < b1) {
+            if (lane_live(blk)) {
+                const size_t off = (size_t(blk) * 64 + size_t(t4) * 16) * 2;
+                VecIO<32>::load(wA + off, wb[slot][0]);
+                VecIO<32>::load(wB + off, wb[slot][1]);
+            } else {
+                #pragma unroll
+                for (int i = 0; i < 8; ++i) { wb[slot][0][i] = 0u; wb[slot][1][i] = 0u; }
             }
         }
     };
+    #pragma unroll
+    for (int d = 0; d < DEPTH; ++d) issue(d, b0 + d);          // weights (constants) travel during all that follows
 
-    int p = blockIdx.x * (kSkinnyThreads / 32) + warp;
-    if (p < npairs) load_group(p, 0);                          // weights travel during the prologue
+    // Everything below reads what earlier kernels of the stream produced.
+    griddep_wait();
 
-    // ---- prologue: X into shared memory as 16-bit ------------------------------------------------
+    // ---- prologue: X into shared memory as 16-bit, rows in [M, Mp) zero --------------------------------
     if (PRO == PRO_RMSNORM) {
-        // forward.hpp:34-56: y = x * rsqrt(mean(x^2) + eps) * w; one warp per row
-        for (int m = warp; m < MT; m += kSkinnyThreads / 32) {
-            T* dst = xs + size_t(m) * K;
-            if (m < a.M) {
-                const float* x = a.X32 + size_t(m) * K;
-                float ss = 0.f;
-                for (int i = lane * 4; i < K; i += 128) {
-                    const float4 v = *reinterpret_cast<const float4*>(x + i);
-                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        // forward.hpp:34-56: y = x * rsqrt(mean(x^2) + eps) * w.  8 / Mp warps share a row; each keeps
+        // up to 4 quads per lane in registers between the sum of squares and the scaling.
+        constexpr int CACHE = 4;
+        const int wpr = kSkinnyWarps / Mp;                      // warps per row
+        const int m = warp / wpr, part = warp % wpr;
+        const int quads = K / 4, qper = (quads + wpr - 1) / wpr;
+        const int q0 = part * qper, q1 = min(q0 + qper, quads);
+        const float* x = a.X32 + size_t(m) * K;
+        const T* nw = static_cast<const T*>(a.norm_w);
+        T* dst = xs + size_t(m) * xstride;
+        float4 cx[CACHE]; uint2 cw[CACHE];
+        float ss = 0.f;
+        if (m < a.M) {
+            #pragma unroll
+            for (int it = 0; it < CACHE; ++it) {
+                const int q = q0 + lane + 32 * it;
+                if (q < q1) {
+                    cx[it] = *reinterpret_cast<const float4*>(x + 4 * q);
+                    cw[it] = *reinterpret_cast<const uint2*>(nw + 4 * q);
+                    ss += cx[it].x * cx[it].x + cx[it].y * cx[it].y + cx[it].z * cx[it].z + cx[it].w * cx[it].w;
                 }
-                ss = wave::dpp::reduce_sum(ss);
-                const float inv = rsqrtf(ss / K + a.eps);
-                const T* nw = static_cast<const T*>(a.norm_w);
-                for (int i = lane * 4; i < K; i += 128) {
-                    const float4 v = *reinterpret_cast<const float4*>(x + i);
-                    dst[i]     = from_float<T>(v.x * inv * to_float(nw[i]));
-                    dst[i + 1] = from_float<T>(v.y * inv * to_float(nw[i + 1]));
-                    dst[i + 2] = from_float<T>(v.z * inv * to_float(nw[i + 2]));
-                    dst[i + 3] = from_float<T>(v.w * inv * to_float(nw[i + 3]));
-                }
-            } else {
-                for (int i = lane; i < K; i += 32) dst[i] = from_float<T>(0.f);
             }
+            for (int q = q0 + lane + 32 * CACHE; q < q1; q += 32) {
+                const float4 v = *reinterpret_cast<const float4*>(x + 4 * q);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+        }
+        ss = wave::dpp::reduce_sum(ss);
+        if (lane == 0) part_ss[warp] = ss;
+        __syncthreads();
+        float tot = 0.f;
+        for (int w = 0; w < wpr; ++w) tot += part_ss[m * wpr + w];
+        const float inv = rsqrtf(tot / K + a.eps);
+        auto put = [&](int q, const float4& v, const uint2& wv) {
+            const T* w4 = reinterpret_cast<const T*>(&wv);
+            uint2 o;
+            o.x = pack2<T>(v.x * inv * to_float(w4[0]), v.y * inv * to_float(w4[1]));
+            o.y = pack2<T>(v.z * inv * to_float(w4[2]), v.w * inv * to_float(w4[3]));
+            *reinterpret_cast<uint2*>(dst + 4 * q) = o;
+        };
+        if (m < a.M) {
+            #pragma unroll
+            for (int it = 0; it < CACHE; ++it) {
+                const int q = q0 + lane + 32 * it;
+                if (q < q1) put(q, cx[it], cw[it]);
+            }
+            for (int q = q0 + lane + 32 * CACHE; q < q1; q += 32)
+                put(q, *reinterpret_cast<const float4*>(x + 4 * q), *reinterpret_cast<const uint2*>(nw + 4 * q));
+        } else {
+            for (int q = q0 + lane; q < q1; q += 32) *reinterpret_cast<uint2*>(dst + 4 * q) = make_uint2(0u, 0u);
         }
     } else {
         const int vec_per_row = K / 8;                          // 16-byte vectors
-        for (int i = threadIdx.x; i < MT * vec_per_row; i += kSkinnyThreads) {
+        for (int i = threadIdx.x; i < Mp * vec_per_row; i += kSkinnyThreads) {
             const int m = i / vec_per_row, v = i % vec_per_row;
             uint4 val = make_uint4(0u, 0u, 0u, 0u);
             if (m < a.M) val = *reinterpret_cast<const uint4*>(static_cast<const T*>(a.X16) + size_t(m) * a.ldx + size_t(v) * 8);
-            *reinterpret_cast<uint4*>(xs + size_t(m) * K + size_t(v) * 8) = val;
+            *reinterpret_cast<uint4*>(xs + size_t(m) * xstride + size_t(v) * 8) = val;
         }
     }
     __syncthreads();
 
-    // ---- stream the rows of W ---------------------------------------------------------------------
-    for (; p < npairs; p += nwarps) {
-        size_t r0, r1; bool has1;
-        rows_of(p, r0, r1, has1);
-        float acc[2][MT];
+    // ---- stream this warp's share of the 16 rows through the tensor cores ---------------------------
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const T* xrow = xs + size_t(g) * xstride + t4 * 16;        // B fragment: X row g, the lane's 16 columns
+    for (int base = b0; base < b1; base += DEPTH) {
         #pragma unroll
-        for (int m = 0; m < MT; ++m) { acc[0][m] = 0.f; acc[1][m] = 0.f; }
-        for (int c0 = 0; c0 < nchunk; c0 += CH) {
-            if (c0 > 0) load_group(p, c0);
-            #pragma unroll
-            for (int c = 0; c < CH; ++c) {
-                const int k0 = ((c0 + c) * 32 + lane) * 16;
-                if (c0 + c < nchunk && k0 < K) {
-                    float w0[16], w1[16];
-                    #pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        unpack_pair<T>(wreg[0][c][i], w0[2 * i], w0[2 * i + 1]);
-                        if (has1) unpack_pair<T>(wreg[1][c][i], w1[2 * i], w1[2 * i + 1]);
-                        else      { w1[2 * i] = 0.f; w1[2 * i + 1] = 0.f; }
-                    }
-                    #pragma unroll
-                    for (int m = 0; m < MT; ++m) {
-                        const uint4* xp = reinterpret_cast<const uint4*>(xs + size_t(m) * K + k0);
-                        const uint4 xa = xp[0], xb = xp[1];
-                        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-                        #pragma unroll
-                        for (int i = 0; i < 8; ++i) {
-                            float x0, x1;
-                            unpack_pair<T>(xw[i], x0, x1);
-                            acc[0][m] = fmaf(w0[2 * i], x0, acc[0][m]); acc[0][m] = fmaf(w0[2 * i + 1], x1, acc[0][m]);
-                            acc[1][m] = fmaf(w1[2 * i], x0, acc[1][m]); acc[1][m] = fmaf(w1[2 * i + 1], x1, acc[1][m]);
-                        }
-                    }
+        for (int d = 0; d < DEPTH; ++d) {
+            const int blk = base + d;
+            if (blk < b1) {                                     // warp-uniform
+                uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
+                if (g < Mp && lane_live(blk)) {                 // columns of B past Mp are zero: no row to read
+                    const uint4* xp = reinterpret_cast<const uint4*>(xrow + size_t(blk) * 64);
+                    xa = xp[0]; xb = xp[1];
+                }
+                const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                #pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    const uint32_t af[4] = {wb[d][0][2 * s], wb[d][1][2 * s], wb[d][0][2 * s + 1], wb[d][1][2 * s + 1]};
+                    mma_16816<T>(acc, af, xw[2 * s], xw[2 * s + 1]);
                 }
             }
+            issue(d, blk + DEPTH);
         }
-        // issue the next pair's first loads before the reduction
-        const int pn = p + nwarps;
-        #pragma unroll
-        for (int m = 0; m < MT; ++m) {
-            acc[0][m] = wave::dpp::reduce_sum(acc[0][m]);
-            acc[1][m] = wave::dpp::reduce_sum(acc[1][m]);
-        }
-        if (pn < npairs) load_group(pn, 0);
-        if (lane == 0) {
+    }
+
+    // ---- the 8 warps' partial sums meet; epilogue -----------------------------------------------------
+    *reinterpret_cast<float4*>(&red[warp][lane][0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    __syncthreads();
+    if (EPI == EPI_SILU16) {
+        if (threadIdx.x < 64) {
+            const int l = threadIdx.x % 32, sel = threadIdx.x / 32;
+            float gate = 0.f, up = 0.f;
             #pragma unroll
-            for (int m = 0; m < MT; ++m) {
-                if (m >= a.M) break;
-                if (EPI == EPI_SILU16) {
-                    const float g = acc[0][m], u = acc[1][m];
-                    static_cast<T*>(a.out)[size_t(m) * a.ldo + p] = from_float<T>((g / (1.f + expf(-g))) * u);
-                } else {
-                    #pragma unroll
-                    for (int r = 0; r < 2; ++r) {
-                        if (r == 1 && !has1) break;
-                        const size_t idx = size_t(m) * a.ldo + (r ? r1 : r0);
-                        if (EPI == EPI_STORE16)      static_cast<T*>(a.out)[idx] = from_float<T>(acc[r][m]);
-                        else if (EPI == EPI_STORE32) static_cast<float*>(a.out)[idx] = acc[r][m];
-                        else                         static_cast<float*>(a.out)[idx] += acc[r][m];
-                    }
-                }
-            }
+            for (int w = 0; w < kSkinnyWarps; ++w) { gate += red[w][l][sel]; up += red[w][l][2 + sel]; }
+            const int m = 2 * (l % 4) + sel, p = blockIdx.x * 8 + l / 4;
+            if (m < a.M && p < a.N)
+                static_cast<T*>(a.out)[size_t(m) * a.ldo + p] = from_float<T>((gate / (1.f + expf(-gate))) * up);
+        }
+    } else if (threadIdx.x < 128) {
+        const int l = threadIdx.x % 32, c = threadIdx.x / 32;
+        float v = 0.f;
+        #pragma unroll
+        for (int w = 0; w < kSkinnyWarps; ++w) v += red[w][l][c];
+        const int m = 2 * (l % 4) + (c & 1), n = blockIdx.x * 16 + l / 4 + 8 * (c >> 1);
+        if (m < a.M && n < a.N) {
+            const size_t idx = size_t(m) * a.ldo + n;
+            if (EPI == EPI_STORE16)      static_cast<T*>(a.out)[idx] = from_float<T>(v);
+            else if (EPI == EPI_STORE32) static_cast<float*>(a.out)[idx] = v;
+            else                         static_cast<float*>(a.out)[idx] += v;
         }
     }
 }
 
 // Launch: returns B200P_E_RANGE when the shape is outside the kernel's domain (the caller then
-// takes the library GEMM).  K must be a multiple of 16 (32-byte rows of W and X), ldx of 8.
+// takes the library GEMM).  K must be a multiple of 16 (32-byte steps along the rows of W and X),
+// ldx of 8, W 32-byte aligned.
 template <typename T, int PRO, int EPI>
 int launch_skinny(const SkinnyArgs& a, cudaStream_t st) {
-    if (a.M < 1 || a.M > kSkinnyMaxM || a.K % 16 != 0 || a.N < 1) return B200P_E_RANGE;
+    if (a.M < 1 || a.M > kSkinnyMaxM || a.K < 16 || a.K % 16 != 0 || a.N < 1) return B200P_E_RANGE;
     if (PRO == PRO_PLAIN && (a.ldx % 8 != 0 || !aligned(a.X16, 16))) return B200P_E_RANGE;
+    if (PRO == PRO_RMSNORM && (!aligned(a.X32, 16) || !aligned(a.norm_w, 8))) return B200P_E_RANGE;
     if (!aligned(a.W, 32)) return B200P_E_RANGE;
-    const int MT = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
-    const size_t smem = size_t(MT) * a.K * 2;
+    const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
+    const size_t smem = size_t(Mp) * (a.K + kSkinnyXPad) * 2;
     if (smem > 200 * 1024) return B200P_E_RANGE;
-    const int npairs = EPI == EPI_SILU16 ? a.N : (a.N + 1) / 2;
-    const int sms = sm_count() > 0 ? sm_count() : 148;
-    int grid = (npairs + 7) / 8;
-    if (grid > 2 * sms) grid = 2 * sms;
-    auto go = [&](auto kern) -> int {
-        if (smem > 48 * 1024) {
+    const int grid = EPI == EPI_SILU16 ? (a.N + 7) / 8 : (a.N + 15) / 16;
+    auto kern = skinny_gemm_kernel<T, PRO, EPI>;
+    if (smem > 40 * 1024) {                                     // static + dynamic beyond 48 KB needs the opt-in
+        static size_t granted[64] = {};                         // per device, per instantiation
+        int dev = 0; cudaGetDevice(&dev);
+        if (dev >= 0 && dev < 64 && granted[dev] < smem) {
             const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
             if (e != cudaSuccess) return int(e);
+            granted[dev] = smem;
         }
-        kern<<<grid, kSkinnyThreads, smem, st>>>(a);
-        return launched();
-    };
-    switch (MT) {
-        case 1: return go(skinny_gemm_kernel<T, 1, PRO, EPI>);
-        case 2: return go(skinny_gemm_kernel<T, 2, PRO, EPI>);
-        case 4: return go(skinny_gemm_kernel<T, 4, PRO, EPI>);
-        default: return go(skinny_gemm_kernel<T, 8, PRO, EPI>);
     }
+    // Launched as a programmatic dependent: the CTAs may start while the previous kernel of the
+    // stream is still draining, fetch their weights, and wait at griddep_wait() for its results.
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(grid); cfg.blockDim = dim3(kSkinnyThreads); cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr; cfg.numAttrs = tuning(KNOB_RUNTIME_PDL, 1) != 0 ? 1 : 0;
+    const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, a);
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    return le == cudaSuccess ? B200P_OK : int(le);
 }
 
 } // namespace b200p
