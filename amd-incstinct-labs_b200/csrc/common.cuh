@@ -20,6 +20,7 @@ enum Knob {
     KNOB_SEG_CTAS_PER_SM,       // resident CTAs per SM for the streaming kernels
     KNOB_SCAN_FP_EXACT,         // 1: reference association for fp scans, 0: fast
     KNOB_DECODE_SPLITS,         // split-KV count override
+    KNOB_DECODE_FUSED_COMBINE,  // 1: the tensor-core decode kernel merges its splits itself, 0: separate combine launch
     KNOB_DECODE_VARIANT,        // 1: tensor-map + mma.sync kernel, 0: bulk-copy + vector kernel
     KNOB_PREFILL_VARIANT,
     KNOB_RUNTIME_GRAPH,         // 1: the runtime replays its decode step as a CUDA graph, 0: launches it every step

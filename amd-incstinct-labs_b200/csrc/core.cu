@@ -13,7 +13,7 @@ namespace {
 std::atomic<int> g_knobs[KNOB_COUNT];
 struct KnobInit { KnobInit() { for (auto& k : g_knobs) k.store(-1); } } g_knob_init;
 const char* const kKnobNames[KNOB_COUNT] = {
-    "seg_vec_bytes", "seg_ctas_per_sm", "scan_fp_exact", "decode_splits", "decode_variant", "prefill_variant",
+    "seg_vec_bytes", "seg_ctas_per_sm", "scan_fp_exact", "decode_splits", "decode_fused_combine", "decode_variant", "prefill_variant",
     "runtime_graph", "runtime_pdl", "runtime_skinny", "scan16_lane",
 };
 constexpr int kMaxDevices = 64;

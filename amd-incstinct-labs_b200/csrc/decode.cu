@@ -69,6 +69,10 @@ struct DecodeParams {
     float scale_log2;             // log2(e) / sqrt(D)
     const int* n_dev;             // non-null: keys = min(*n_dev + n_add, N), read by the kernels (N is then the bound)
     int n_add;
+    // Fused combine (tensor-core kernel, 16-bit output): the last CTA of a (sequence, KV head)
+    // to finish merges that unit's splits and writes o; tickets[batch * nKVH] count arrivals
+    // and reset themselves.  Null: the partials are left for a separate combine launch.
+    void* fused_o; unsigned int* tickets; long long o_batch_stride;
 };
 
 // Key count and keys per split of this launch.  With a device-side count the split
@@ -526,6 +530,44 @@ decode_mma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK
             if (d == 0) { p.part_ml[row * 2] = M; p.part_ml[row * 2 + 1] = L; }
         }
     }
+    if (p.fused_o) {
+        // ---- the last CTA of this (sequence, KV head) merges the unit's splits: the reference's
+        // merge (fa_decode_kernel.hpp:75-92) without a second launch -------------------------------
+        __shared__ int s_last;
+        __threadfence();                                   // this CTA's partials are visible device-wide ...
+        __syncthreads();
+        if (threadIdx.x == 0) {                            // ... before its ticket is
+            unsigned int* tk = p.tickets + size_t(b) * p.nKVH + kvh;
+            const unsigned int t = atomicAdd(tk, 1u);
+            s_last = (t == unsigned(p.splits) - 1u);
+            if (s_last) *tk = 0u;                          // ready for the next launch on this stream
+        }
+        __syncthreads();
+        if (s_last) {
+            __threadfence();
+            constexpr int PER = D / 32;
+            for (int hh = warp; hh < p.group; hh += kDecodeThreads / 32) {
+                const size_t row = size_t(b) * p.nQH + size_t(kvh) * p.group + hh;
+                const float* ml = p.part_ml + row * p.splits * 2;
+                const float* po = p.part_o + row * p.splits * D;
+                float M = kNegBig;
+                for (int s = 0; s < p.splits; ++s) M = fmaxf(M, __ldcg(ml + 2 * s));
+                float L = 0.f, acc[PER];
+                #pragma unroll
+                for (int i = 0; i < PER; ++i) acc[i] = 0.f;
+                for (int s = 0; s < p.splits; ++s) {
+                    const float f = exp2f(__ldcg(ml + 2 * s) - M);
+                    L += f * __ldcg(ml + 2 * s + 1);
+                    #pragma unroll
+                    for (int i = 0; i < PER; ++i) acc[i] += f * __ldcg(po + size_t(s) * D + lane + 32 * i);
+                }
+                const float inv = L > 0.f ? 1.f / L : 1.f;
+                T* orow = static_cast<T*>(p.fused_o) + size_t(b) * p.o_batch_stride + (size_t(kvh) * p.group + hh) * D;
+                #pragma unroll
+                for (int i = 0; i < PER; ++i) orow[lane + 32 * i] = from_float<T>(acc[i] * inv);
+            }
+        }
+    }
     __syncthreads();
     if (threadIdx.x == 0 && s_failed) atomicExch(p.status, 1);
 }
@@ -705,7 +747,7 @@ merge_lse_wait_kernel(const float* slots, const int* flags, int world, int seq, 
 }
 
 // ---- host side ------------------------------------------------------------------------
-struct DecodePlan { int splits, keys_per_split; size_t ws_bytes, off_ml, off_o; };
+struct DecodePlan { int splits, keys_per_split; size_t ws_bytes, off_tickets, off_ml, off_o; };
 
 DecodePlan plan_decode(int D, int N, int nQH, int nKVH, int batch) {
     DecodePlan pl{};
@@ -726,7 +768,8 @@ DecodePlan plan_decode(int D, int N, int nQH, int nKVH, int batch) {
     if (splits < 1) splits = 1;
     pl.splits = splits; pl.keys_per_split = per;
     const size_t rows = size_t(batch) * nQH;
-    pl.off_ml = 256;                                    // [0,256): status word
+    pl.off_tickets = 256;                               // [0,256): status word; then one arrival counter per (sequence, KV head)
+    pl.off_ml = pl.off_tickets + ((size_t(batch) * nKVH * sizeof(unsigned int) + 255) / 256) * 256;
     pl.off_o = pl.off_ml + ((rows * splits * 2 * sizeof(float) + 255) / 256) * 256;
     pl.ws_bytes = pl.off_o + rows * splits * D * sizeof(float);
     return pl;
@@ -822,7 +865,8 @@ int validate_peers(const b200p_peer_exchange* px) {
 
 int run_decode(const b200p_decode_args* a, const void* q, const void* K, const void* V,
                void* o, float* o_f32, float* lse, void* ws, size_t ws_bytes, cudaStream_t st,
-               const b200p_peer_exchange* px = nullptr, int seq = 0, const int* n_dev = nullptr, int n_add = 0) {
+               const b200p_peer_exchange* px = nullptr, int seq = 0, const int* n_dev = nullptr, int n_add = 0,
+               bool prepared = false) {
     if (int e = validate(a)) return e;
     if (!q || !K || !V || (!px && !o && !(o_f32 && lse))) return B200P_E_NULL;
     if (px) {
@@ -851,17 +895,29 @@ int run_decode(const b200p_decode_args* a, const void* q, const void* K, const v
     // K/V rows must start on 16 bytes for the bulk copies
     if ((p.kv_head_stride * 2) % 16 || (p.kv_batch_stride * 2) % 16) return B200P_E_ALIGN;
 
-    cudaError_t ce = cudaMemsetAsync(ws, 0, 4, st);
-    if (ce != cudaSuccess) return int(ce);
     // variant 1 (default): TMA tensor maps + mma.sync; variant 0: bulk copies + vector FMAs.
     // The tensor-core kernel holds the whole group in one M = 16 tile.
     const bool use_mma = tuning(KNOB_DECODE_VARIANT, 1) == 1 && p.group <= 16 && aligned(q, 4);
+    const long long obs = a->o_batch_stride > 0 ? a->o_batch_stride : (long long)a->nQHeads * a->D;
+    // 16-bit output from the tensor-core kernel: the combine is fused into it (last CTA of a unit merges)
+    const bool fused = use_mma && o && !px && tuning(KNOB_DECODE_FUSED_COMBINE, 1) != 0;
+    if (fused) {
+        p.fused_o = o; p.o_batch_stride = obs;
+        p.tickets = reinterpret_cast<unsigned int*>(static_cast<char*>(ws) + pl.off_tickets);
+    }
+    // Clear the status word and the arrival counters, unless the caller keeps the workspace
+    // prepared (both zero before the first launch; the counters reset themselves, and the
+    // status word only ever changes when a bounded wait gives up).
+    if (!prepared) {
+        const cudaError_t ce = cudaMemsetAsync(ws, 0, pl.off_ml, st);
+        if (ce != cudaSuccess) return int(ce);
+    }
     int e;
     if (use_mma) e = a->dtype == B200P_F16 ? launch_decode_mma_d<__half>(p, a, st) : launch_decode_mma_d<__nv_bfloat16>(p, a, st);
     else         e = a->dtype == B200P_F16 ? launch_decode_d<__half>(p, a->D, st) : launch_decode_d<__nv_bfloat16>(p, a->D, st);
     if (e) return e;
+    if (fused) return B200P_OK;
     const int rows = a->batch * a->nQHeads, rps = a->nQHeads;
-    const long long obs = a->o_batch_stride > 0 ? a->o_batch_stride : (long long)a->nQHeads * a->D;
     if (px) {
         PeerTable pt{};
         for (int g = 0; g < px->world; ++g) { pt.slots[g] = px->slots[g]; pt.flags[g] = px->flags[g]; }
@@ -878,6 +934,15 @@ int run_decode(const b200p_decode_args* a, const void* q, const void* K, const v
 }
 
 } // namespace
+
+// For callers inside the library that keep their workspace prepared (status word and arrival
+// counters zero before the first use): decode without the clearing memset, key count by value
+// (n_dev null) or read on the device.
+int decode_prepared(const void* q, const void* K, const void* V, void* o, const b200p_decode_args* a,
+                    const int* n_dev, int n_add, void* ws, size_t ws_bytes, cudaStream_t st) {
+    if (!o) return B200P_E_NULL;
+    return run_decode(a, q, K, V, o, nullptr, nullptr, ws, ws_bytes, st, nullptr, 0, n_dev, n_add, true);
+}
 } // namespace b200p
 
 using namespace b200p;

@@ -33,6 +33,8 @@
 #include <vector>
 
 namespace b200p {
+int decode_prepared(const void* q, const void* K, const void* V, void* o, const b200p_decode_args* a,
+                    const int* n_dev, int n_add, void* ws, size_t ws_bytes, cudaStream_t st);
 int prefill_dispatch_strided(const void* Q, const void* K, const void* V, void* O, const b200p_prefill_cfg* c, int dtype,
                              const b200p_attn_strides* strides, float* debug_s, cudaStream_t st);
 namespace {
@@ -313,9 +315,8 @@ int decode_layer_skinny(b200p_session* s, int li, int pos0, cudaStream_t st, con
         d.D = D; d.N = pos_dev ? s->max_seq : pos0 + 1; d.nQHeads = c.n_heads; d.nKVHeads = c.n_kv_heads; d.stride_kv = s->max_seq;
         d.batch = B; d.dtype = s->dtype; d.kv_batch_stride = (long long)c.n_kv_heads * s->max_seq * D;
         d.key_offset = 0; d.q_batch_stride = W; d.o_batch_stride = qd;
-        const int e = pos_dev ? b200p_attn_decode_dyn(s->qkv, kc, vc, s->attn, &d, pos_dev, 1, s->decode_ws, s->decode_ws_bytes, st)
-                              : b200p_attn_decode(s->qkv, kc, vc, s->attn, &d, s->decode_ws, s->decode_ws_bytes, st);
-        if (e) return e;
+        // the session's workspace stays prepared (zeroed at creation): no clearing memset per layer
+        if (int e = decode_prepared(s->qkv, kc, vc, s->attn, &d, pos_dev, 1, s->decode_ws, s->decode_ws_bytes, st)) return e;
     }
     // 6. O projection accumulated into the residual stream
     a = SkinnyArgs{}; a.M = B; a.eps = 1e-6f;
@@ -614,6 +615,7 @@ int build(b200p_session* s, const b200p_model_weights* w) {
     }
     s->decode_ws_bytes = need * 2;
     if ((e = s->alloc(&s->decode_ws, s->decode_ws_bytes))) return int(e);
+    if ((e = cudaMemset(s->decode_ws, 0, s->decode_ws_bytes))) return int(e);
     if (cublasCreate(&s->blas) != CUBLAS_STATUS_SUCCESS) return int(cudaErrorUnknown);
     return int(cudaDeviceSynchronize());
 }

@@ -11,13 +11,17 @@ pytestmark = pytest.mark.gpu
 TOL = 2e-2
 
 
-@pytest.fixture(params=[1, 0], ids=["mma", "vector"], autouse=True)
+@pytest.fixture(params=[(1, 1), (1, 0), (0, 1)], ids=["mma-fused-combine", "mma-separate-combine", "vector"], autouse=True)
 def decode_variant(b200p, request):
-    """Every test runs on both decode kernels: 1 = TMA tensor maps + mma.sync (default),
-    0 = bulk copies + vector FMAs."""
-    b200p.set_tuning("decode_variant", request.param)
-    yield request.param
+    """Every test runs on both decode kernels: 1 = TMA tensor maps + mma.sync (default; with the
+    split merge fused into the kernel, and with the separate combine launch), 0 = bulk copies +
+    vector FMAs."""
+    variant, fused = request.param
+    b200p.set_tuning("decode_variant", variant)
+    b200p.set_tuning("decode_fused_combine", fused)
+    yield variant
     b200p.set_tuning("decode_variant", -1)
+    b200p.set_tuning("decode_fused_combine", -1)
 
 
 def dev16(torch, f32, kind):
