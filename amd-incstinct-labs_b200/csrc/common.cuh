@@ -14,6 +14,8 @@ extern std::atomic<unsigned long long> g_launches;
 int sm_count();
 // Value of a tuning knob (see b200p_set_tuning), or `dflt` when unset (< 0).
 int tuning(int knob, int dflt);
+// Counts b200p_set_tuning calls: anything that bakes knob values in (a captured graph) compares it.
+unsigned tuning_epoch();
 
 enum Knob {
     KNOB_SEG_VEC_BYTES = 0,     // 16 or 32: bytes one lane loads per instruction
@@ -25,6 +27,7 @@ enum Knob {
     KNOB_PREFILL_VARIANT,
     KNOB_RUNTIME_GRAPH,         // 1: the runtime replays its decode step as a CUDA graph, 0: launches it every step
     KNOB_RUNTIME_PDL,           // 1: skinny kernels launch as programmatic dependents (weights prefetched before the wait)
+    KNOB_RUNTIME_ROPE_FUSED,    // 1: RoPE + KV scatter in the Q/K/V projection's epilogue, 0: separate kernel
     KNOB_RUNTIME_SKINNY,        // 1: decode-step projections on skinny_gemm_kernel, 0: library GEMMs
     KNOB_SCAN16_LANE,           // 1: 16-bit scans hold a whole segment per lane, 0: four lanes per segment
     KNOB_COUNT

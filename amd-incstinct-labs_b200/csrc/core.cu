@@ -11,10 +11,11 @@ std::atomic<unsigned long long> g_launches{0};
 
 namespace {
 std::atomic<int> g_knobs[KNOB_COUNT];
+std::atomic<unsigned> g_tuning_epoch{0};
 struct KnobInit { KnobInit() { for (auto& k : g_knobs) k.store(-1); } } g_knob_init;
 const char* const kKnobNames[KNOB_COUNT] = {
     "seg_vec_bytes", "seg_ctas_per_sm", "scan_fp_exact", "decode_splits", "decode_fused_combine", "decode_variant", "prefill_variant",
-    "runtime_graph", "runtime_pdl", "runtime_skinny", "scan16_lane",
+    "runtime_graph", "runtime_pdl", "runtime_rope_fused", "runtime_skinny", "scan16_lane",
 };
 constexpr int kMaxDevices = 64;
 std::atomic<int> g_sms[kMaxDevices];
@@ -30,6 +31,8 @@ int sm_count() {
     g_sms[dev].store(sms, std::memory_order_relaxed);
     return sms;
 }
+
+unsigned tuning_epoch() { return g_tuning_epoch.load(std::memory_order_relaxed); }
 
 int tuning(int knob, int dflt) {
     const int v = g_knobs[knob].load(std::memory_order_relaxed);
@@ -65,7 +68,7 @@ extern "C" unsigned long long b200p_launch_count(void) { return g_launches.load(
 extern "C" int b200p_set_tuning(const char* key, int value) {
     if (!key) return INT_MIN;
     for (int i = 0; i < KNOB_COUNT; ++i) {
-        if (std::strcmp(key, kKnobNames[i]) == 0) return g_knobs[i].exchange(value);
+        if (std::strcmp(key, kKnobNames[i]) == 0) { g_tuning_epoch.fetch_add(1); return g_knobs[i].exchange(value); }
     }
     return INT_MIN;
 }

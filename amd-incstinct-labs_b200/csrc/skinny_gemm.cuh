@@ -47,7 +47,21 @@
 namespace b200p {
 
 enum SkinnyPrologue { PRO_PLAIN = 0, PRO_RMSNORM = 1 };
-enum SkinnyEpilogue { EPI_STORE16 = 0, EPI_ACC32 = 1, EPI_STORE32 = 2, EPI_SILU16 = 3 };
+enum SkinnyEpilogue { EPI_STORE16 = 0, EPI_ACC32 = 1, EPI_STORE32 = 2, EPI_SILU16 = 3, EPI_ROPE = 4 };
+
+// EPI_ROPE: W is the concatenated Q/K/V projection; the epilogue is the reference's bias add,
+// rotate-half RoPE and KV-cache scatter (forward.hpp:135-148, 211-224; rocblas_gemm.hpp:56-63)
+// for ONE new token per sequence (row m of X is sequence m).  A CTA takes 8 rows d and the 8
+// rows d + D/2 of one head, so each rotation pair meets in one thread.
+struct SkinnyRope {
+    const void*  bias;      // [N] 16-bit or null
+    const float* cos_t;     // [max_seq][D/2]
+    const float* sin_t;
+    void* kcache;           // [batch][nKVH][max_seq][D] 16-bit
+    void* vcache;
+    const int* pos_dev;     // position of the new token, read on the device (null: pos0)
+    int pos0, nQH, nKVH, D, max_seq;
+};
 
 struct SkinnyArgs {
     const void*  W;        // [N][K] 16-bit (EPI_SILU16: [2N][K], gate rows then up rows)
@@ -57,6 +71,7 @@ struct SkinnyArgs {
     void*        out;      // [M][ldo] 16-bit or fp32
     int M, N, K, ldx, ldo;
     float eps;
+    SkinnyRope rope;       // EPI_ROPE only
 };
 
 constexpr int kSkinnyThreads = 256;
@@ -65,55 +80,73 @@ constexpr int kSkinnyMaxM = 8;
 constexpr int kSkinnyDepth = 4;       // 64-column blocks in flight per warp
 constexpr int kSkinnyXPad = 8;        // elements: X rows are 16 bytes longer than K
 
-template <typename T, int PRO, int EPI>
+// R = rows of W per lane: 2 -> a CTA step covers 16 rows (accumulator rows g and g + 8), 4 column
+// blocks in flight; 1 -> 8 rows (the upper half of the A operand is zero), 8 blocks in flight: twice
+// the CTAs for matrices too small to fill the GPU otherwise.
+template <typename T, int PRO, int EPI, int R>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
 skinny_gemm_kernel(const SkinnyArgs a) {
     griddep_launch_dependents();
     extern __shared__ __align__(16) unsigned char skinny_smem[];
     T* xs = reinterpret_cast<T*>(skinny_smem);                 // [Mp][K + pad]
-    __shared__ float red[kSkinnyWarps][32][4];
+    __shared__ float red[2][kSkinnyWarps][32][4];               // double-buffered by group
     __shared__ float part_ss[kSkinnyWarps];
-    constexpr int DEPTH = kSkinnyDepth;
+    constexpr int DEPTH = 8 / R;
+    static_assert(R == 2 || (EPI != EPI_SILU16 && EPI != EPI_ROPE), "paired epilogues need both halves");
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int g = lane / 4, t4 = lane % 4;
     const int K = a.K, xstride = K + kSkinnyXPad;
     const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;   // rows of X kept in shared memory
 
-    // the CTA's rows: half 0 -> accumulator rows g, half 1 -> rows g + 8
-    size_t rowA, rowB;
-    if (EPI == EPI_SILU16) {
-        const int p = min(blockIdx.x * 8 + g, a.N - 1);        // pair index: gate row p, up row N + p
-        rowA = size_t(p); rowB = size_t(a.N) + size_t(p);
-    } else {
-        rowA = size_t(min(blockIdx.x * 16 + g, a.N - 1));
-        rowB = size_t(min(blockIdx.x * 16 + g + 8, a.N - 1));
-    }
-    const char* wA = static_cast<const char*>(a.W) + rowA * size_t(K) * 2;
-    const char* wB = static_cast<const char*>(a.W) + rowB * size_t(K) * 2;
+    // Row groups: group `grp` is 8 * R rows of W (8 row pairs for the paired epilogues); the CTA
+    // takes groups blockIdx.x, blockIdx.x + gridDim.x, ...
+    const int ngroups = (EPI == EPI_SILU16) ? (a.N + 7) / 8 : (a.N + 8 * R - 1) / (8 * R);
+    auto row_ptrs = [&](int grp, const char*& wA, const char*& wB) {
+        size_t rowA, rowB;
+        if (EPI == EPI_SILU16) {
+            const int p = min(grp * 8 + g, a.N - 1);            // pair index: gate row p, up row N + p
+            rowA = size_t(p); rowB = size_t(a.N) + size_t(p);
+        } else if (EPI == EPI_ROPE) {
+            const int cph = a.rope.D / 16;                      // groups per head
+            rowA = size_t(grp / cph) * a.rope.D + size_t(grp % cph) * 8 + g;
+            rowB = rowA + a.rope.D / 2;
+        } else {
+            rowA = size_t(min(grp * 8 * R + g, a.N - 1));
+            rowB = size_t(min(grp * 8 * R + g + 8, a.N - 1));
+        }
+        wA = static_cast<const char*>(a.W) + rowA * size_t(K) * 2;
+        wB = static_cast<const char*>(a.W) + rowB * size_t(K) * 2;
+    };
 
     // this warp's share of K, in blocks of 64 columns
     const int nblk = (K + 63) / 64;
     const int per = (nblk + kSkinnyWarps - 1) / kSkinnyWarps;
     const int b0 = warp * per, b1 = min(b0 + per, nblk);
+    const int nb = max(b1 - b0, 0);                             // blocks per group for this warp
 
-    uint32_t wb[DEPTH][2][8];
+    uint32_t wb[DEPTH][R][8];
     // A block is taken by the whole warp or not at all (mma.sync needs every lane); a lane whose 16
     // columns lie past K (K not a multiple of 64) contributes zeros instead of loading.
     auto lane_live = [&](int blk) { return blk * 64 + t4 * 16 < K; };
-    auto issue = [&](int slot, int blk) {
-        if (blk < b1) {
+    auto issue = [&](int slot, int grp, int j) {               // block j of this warp's share, for group grp
+        if (grp < ngroups && j < nb) {
+            const int blk = b0 + j;
             if (lane_live(blk)) {
+                const char *wA, *wB;
+                row_ptrs(grp, wA, wB);
                 const size_t off = (size_t(blk) * 64 + size_t(t4) * 16) * 2;
                 VecIO<32>::load(wA + off, wb[slot][0]);
-                VecIO<32>::load(wB + off, wb[slot][1]);
+                if (R == 2) VecIO<32>::load(wB + off, wb[slot][R - 1]);
             } else {
                 #pragma unroll
-                for (int i = 0; i < 8; ++i) { wb[slot][0][i] = 0u; wb[slot][1][i] = 0u; }
+                for (int r = 0; r < R; ++r)
+                    #pragma unroll
+                    for (int i = 0; i < 8; ++i) wb[slot][r][i] = 0u;
             }
         }
     };
     #pragma unroll
-    for (int d = 0; d < DEPTH; ++d) issue(d, b0 + d);          // weights (constants) travel during all that follows
+    for (int d = 0; d < DEPTH; ++d) issue(d, blockIdx.x, d);    // weights (constants) travel during all that follows
 
     // Everything below reads what earlier kernels of the stream produced.
     griddep_wait();
@@ -182,54 +215,96 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     }
     __syncthreads();
 
-    // ---- stream this warp's share of the 16 rows through the tensor cores ---------------------------
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    // ---- stream the CTA's row groups through the tensor cores ------------------------------------------
     const T* xrow = xs + size_t(g) * xstride + t4 * 16;        // B fragment: X row g, the lane's 16 columns
-    for (int base = b0; base < b1; base += DEPTH) {
-        #pragma unroll
-        for (int d = 0; d < DEPTH; ++d) {
-            const int blk = base + d;
-            if (blk < b1) {                                     // warp-uniform
-                uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
-                if (g < Mp && lane_live(blk)) {                 // columns of B past Mp are zero: no row to read
-                    const uint4* xp = reinterpret_cast<const uint4*>(xrow + size_t(blk) * 64);
-                    xa = xp[0]; xb = xp[1];
-                }
-                const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
-                #pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    const uint32_t af[4] = {wb[d][0][2 * s], wb[d][1][2 * s], wb[d][0][2 * s + 1], wb[d][1][2 * s + 1]};
-                    mma_16816<T>(acc, af, xw[2 * s], xw[2 * s + 1]);
+    int parity = 0;
+    for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x, parity ^= 1) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int jb = 0; jb < nb; jb += DEPTH) {
+            #pragma unroll
+            for (int d = 0; d < DEPTH; ++d) {
+                const int j = jb + d;
+                if (j < nb) {                                   // warp-uniform
+                    const int blk = b0 + j;
+                    uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
+                    if (g < Mp && lane_live(blk)) {             // columns of B past Mp are zero: no row to read
+                        const uint4* xp = reinterpret_cast<const uint4*>(xrow + size_t(blk) * 64);
+                        xa = xp[0]; xb = xp[1];
+                    }
+                    const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                    #pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+                        const uint32_t af[4] = {wb[d][0][2 * s], R == 2 ? wb[d][R - 1][2 * s] : 0u,
+                                                wb[d][0][2 * s + 1], R == 2 ? wb[d][R - 1][2 * s + 1] : 0u};
+                        mma_16816<T>(acc, af, xw[2 * s], xw[2 * s + 1]);
+                    }
+                    // the slot is free: next block of this group that maps to it, else the next group's
+                    if (j + DEPTH < nb) issue(d, grp, j + DEPTH);
+                    else                issue(d, grp + gridDim.x, d);
                 }
             }
-            issue(d, blk + DEPTH);
         }
-    }
 
-    // ---- the 8 warps' partial sums meet; epilogue -----------------------------------------------------
-    *reinterpret_cast<float4*>(&red[warp][lane][0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-    __syncthreads();
-    if (EPI == EPI_SILU16) {
-        if (threadIdx.x < 64) {
-            const int l = threadIdx.x % 32, sel = threadIdx.x / 32;
-            float gate = 0.f, up = 0.f;
+        // ---- the 8 warps' partial sums meet; epilogue (the next group's loads are in flight) ---------
+        *reinterpret_cast<float4*>(&red[parity][warp][lane][0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        __syncthreads();
+        if (EPI == EPI_SILU16) {
+            if (threadIdx.x < 64) {
+                const int l = threadIdx.x % 32, sel = threadIdx.x / 32;
+                float gate = 0.f, up = 0.f;
+                #pragma unroll
+                for (int w = 0; w < kSkinnyWarps; ++w) { gate += red[parity][w][l][sel]; up += red[parity][w][l][2 + sel]; }
+                const int m = 2 * (l % 4) + sel, p = grp * 8 + l / 4;
+                if (m < a.M && p < a.N)
+                    static_cast<T*>(a.out)[size_t(m) * a.ldo + p] = from_float<T>((gate / (1.f + expf(-gate))) * up);
+            }
+        } else if (EPI == EPI_ROPE) {
+            if (threadIdx.x < 64) {
+                const SkinnyRope& r = a.rope;
+                const int l = threadIdx.x % 32, sel = threadIdx.x / 32;
+                float x0 = 0.f, x1 = 0.f;
+                #pragma unroll
+                for (int w = 0; w < kSkinnyWarps; ++w) { x0 += red[parity][w][l][sel]; x1 += red[parity][w][l][2 + sel]; }
+                const int m = 2 * (l % 4) + sel;
+                if (m < a.M) {
+                    const int cph = r.D / 16, half = r.D / 2;
+                    const int slot = grp / cph, d = (grp % cph) * 8 + l / 4;
+                    x0 = to_float(from_float<T>(x0)); x1 = to_float(from_float<T>(x1));      // the projection's 16-bit output
+                    if (r.bias) {
+                        const T* bias = static_cast<const T*>(r.bias);
+                        x0 = to_float(from_float<T>(x0 + to_float(bias[slot * r.D + d])));
+                        x1 = to_float(from_float<T>(x1 + to_float(bias[slot * r.D + d + half])));
+                    }
+                    const int pos = r.pos_dev ? min(*r.pos_dev, r.max_seq - 1) : r.pos0;
+                    if (slot < r.nQH + r.nKVH) {                  // q or k: rotate
+                        const float c = r.cos_t[size_t(pos) * half + d], sn = r.sin_t[size_t(pos) * half + d];
+                        const float y0 = x0 * c - x1 * sn, y1 = x1 * c + x0 * sn;
+                        x0 = y0; x1 = y1;
+                    }
+                    const T o0 = from_float<T>(x0), o1 = from_float<T>(x1);
+                    if (slot < r.nQH) {                           // q stays in the token-major buffer
+                        T* row = static_cast<T*>(a.out) + size_t(m) * a.ldo + size_t(slot) * r.D;
+                        row[d] = o0; row[d + half] = o1;
+                    } else {                                      // k or v: into cache[m][kvh][pos][:]
+                        const bool is_k = slot < r.nQH + r.nKVH;
+                        const int kvh = is_k ? slot - r.nQH : slot - r.nQH - r.nKVH;
+                        T* dst = static_cast<T*>(is_k ? r.kcache : r.vcache) + ((size_t(m) * r.nKVH + kvh) * r.max_seq + pos) * r.D;
+                        dst[d] = o0; dst[d + half] = o1;
+                    }
+                }
+            }
+        } else if (threadIdx.x < 64 * R) {
+            const int l = threadIdx.x % 32, c = threadIdx.x / 32;
+            float v = 0.f;
             #pragma unroll
-            for (int w = 0; w < kSkinnyWarps; ++w) { gate += red[w][l][sel]; up += red[w][l][2 + sel]; }
-            const int m = 2 * (l % 4) + sel, p = blockIdx.x * 8 + l / 4;
-            if (m < a.M && p < a.N)
-                static_cast<T*>(a.out)[size_t(m) * a.ldo + p] = from_float<T>((gate / (1.f + expf(-gate))) * up);
-        }
-    } else if (threadIdx.x < 128) {
-        const int l = threadIdx.x % 32, c = threadIdx.x / 32;
-        float v = 0.f;
-        #pragma unroll
-        for (int w = 0; w < kSkinnyWarps; ++w) v += red[w][l][c];
-        const int m = 2 * (l % 4) + (c & 1), n = blockIdx.x * 16 + l / 4 + 8 * (c >> 1);
-        if (m < a.M && n < a.N) {
-            const size_t idx = size_t(m) * a.ldo + n;
-            if (EPI == EPI_STORE16)      static_cast<T*>(a.out)[idx] = from_float<T>(v);
-            else if (EPI == EPI_STORE32) static_cast<float*>(a.out)[idx] = v;
-            else                         static_cast<float*>(a.out)[idx] += v;
+            for (int w = 0; w < kSkinnyWarps; ++w) v += red[parity][w][l][c];
+            const int m = 2 * (l % 4) + (c & 1), n = grp * 8 * R + l / 4 + 8 * (c >> 1);
+            if (m < a.M && n < a.N) {
+                const size_t idx = size_t(m) * a.ldo + n;
+                if (EPI == EPI_STORE16)      static_cast<T*>(a.out)[idx] = from_float<T>(v);
+                else if (EPI == EPI_STORE32) static_cast<float*>(a.out)[idx] = v;
+                else                         static_cast<float*>(a.out)[idx] += v;
+            }
         }
     }
 }
@@ -246,16 +321,18 @@ int launch_skinny(const SkinnyArgs& a, cudaStream_t st) {
     const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
     const size_t smem = size_t(Mp) * (a.K + kSkinnyXPad) * 2;
     if (smem > 200 * 1024) return B200P_E_RANGE;
-    const int grid = EPI == EPI_SILU16 ? (a.N + 7) / 8 : (a.N + 15) / 16;
-    auto kern = skinny_gemm_kernel<T, PRO, EPI>;
-    if (smem > 40 * 1024) {                                     // static + dynamic beyond 48 KB needs the opt-in
-        static size_t granted[64] = {};                         // per device, per instantiation
-        int dev = 0; cudaGetDevice(&dev);
-        if (dev >= 0 && dev < 64 && granted[dev] < smem) {
-            const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
-            if (e != cudaSuccess) return int(e);
-            granted[dev] = smem;
-        }
+    if (EPI == EPI_ROPE && (a.rope.D % 16 != 0 || a.N != (a.rope.nQH + 2 * a.rope.nKVH) * a.rope.D)) return B200P_E_RANGE;
+    const int sms = sm_count() > 0 ? sm_count() : 148;
+    constexpr bool paired = EPI == EPI_SILU16 || EPI == EPI_ROPE;
+    // 8-row groups when 16-row groups would leave a third of the CTA slots (2 per SM) empty
+    const bool half_rows = !paired && (a.N + 15) / 16 < (4 * sms) / 3;
+    const int ngroups = EPI == EPI_SILU16 ? (a.N + 7) / 8 : half_rows ? (a.N + 7) / 8 : (a.N + 15) / 16;
+    const int grid = ngroups < 2 * sms ? ngroups : 2 * sms;      // CTAs loop over their groups, loads running ahead
+    void (*kern)(SkinnyArgs) = skinny_gemm_kernel<T, PRO, EPI, 2>;
+    if constexpr (!paired) { if (half_rows) kern = skinny_gemm_kernel<T, PRO, EPI, 1>; }
+    if (smem > 36 * 1024) {                                     // static (8 KB) + dynamic beyond 48 KB needs the opt-in
+        const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
+        if (e != cudaSuccess) return int(e);
     }
     // Launched as a programmatic dependent: the CTAs may start while the previous kernel of the
     // stream is still draining, fetch their weights, and wait at griddep_wait() for its results.
