@@ -73,6 +73,7 @@ struct DecodeParams {
     // to finish merges that unit's splits and writes o; tickets[batch * nKVH] count arrivals
     // and reset themselves.  Null: the partials are left for a separate combine launch.
     void* fused_o; unsigned int* tickets; long long o_batch_stride;
+    int pdl;                      // host only: launch the tensor-core kernel as a programmatic dependent
 };
 
 // Key count and keys per split of this launch.  With a device-side count the split
@@ -372,11 +373,6 @@ decode_mma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK
     const int split = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     griddep_launch_dependents();                  // a programmatic dependent may begin its own prefetch
-    int N, per;
-    decode_extent(p, N, per);
-    const int k0 = min(split * per, N);
-    const int k1 = min(k0 + per, N);
-    const int ntiles = (k1 - k0 + TK - 1) / TK;
 
     if (threadIdx.x == 0) {
         s_failed = 0;
@@ -384,6 +380,14 @@ decode_mma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK
         dme::mbar_init_fence();
     }
     __syncthreads();
+    // Launched as a programmatic dependent (the runtime's decode step) the CTA is resident and set
+    // up by now; everything it reads from memory was produced by earlier kernels of the stream.
+    griddep_wait();
+    int N, per;
+    decode_extent(p, N, per);
+    const int k0 = min(split * per, N);
+    const int k1 = min(k0 + per, N);
+    const int ntiles = (k1 - k0 + TK - 1) / TK;
 
     if (warp == kConsumerWarps) {
         if (lane == 0) {
@@ -836,6 +840,17 @@ int launch_decode_mma(const DecodeParams& p, const b200p_decode_args* a, cudaStr
         attr_set[dev] = true;
     }
     dim3 grid(p.splits, p.nKVH, p.batch);
+    if (p.pdl) {
+        cudaLaunchConfig_t cfg{};
+        cfg.gridDim = grid; cfg.blockDim = dim3(kDecodeThreads); cfg.dynamicSmemBytes = Sh::SMEM_BYTES; cfg.stream = st;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, p, mk, mv);
+        g_launches.fetch_add(1, std::memory_order_relaxed);
+        return le == cudaSuccess ? B200P_OK : int(le);
+    }
     kern<<<grid, kDecodeThreads, Sh::SMEM_BYTES, st>>>(p, mk, mv);
     return launched();
 }
@@ -901,6 +916,7 @@ int run_decode(const b200p_decode_args* a, const void* q, const void* K, const v
     const long long obs = a->o_batch_stride > 0 ? a->o_batch_stride : (long long)a->nQHeads * a->D;
     // 16-bit output from the tensor-core kernel: the combine is fused into it (last CTA of a unit merges)
     const bool fused = use_mma && o && !px && tuning(KNOB_DECODE_FUSED_COMBINE, 1) != 0;
+    p.pdl = prepared && fused && tuning(KNOB_RUNTIME_PDL, 1) != 0;     // the runtime's decode step only
     if (fused) {
         p.fused_o = o; p.o_batch_stride = obs;
         p.tickets = reinterpret_cast<unsigned int*>(static_cast<char*>(ws) + pl.off_tickets);

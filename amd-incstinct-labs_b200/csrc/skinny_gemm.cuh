@@ -215,6 +215,15 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     }
     __syncthreads();
 
+    // EPI_ACC32: fetch the first group's residual values now, so the epilogue's read-modify-write
+    // does not start with a trip to L2
+    float prev = 0.f;
+    if (EPI == EPI_ACC32 && threadIdx.x < 64 * R) {
+        const int l = threadIdx.x % 32, c = threadIdx.x / 32;
+        const int m = 2 * (l % 4) + (c & 1), n = int(blockIdx.x) * 8 * R + l / 4 + 8 * (c >> 1);
+        if (m < a.M && n < a.N) prev = static_cast<const float*>(a.out)[size_t(m) * a.ldo + n];
+    }
+
     // ---- stream the CTA's row groups through the tensor cores ------------------------------------------
     const T* xrow = xs + size_t(g) * xstride + t4 * 16;        // B fragment: X row g, the lane's 16 columns
     int parity = 0;
@@ -303,6 +312,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
                 const size_t idx = size_t(m) * a.ldo + n;
                 if (EPI == EPI_STORE16)      static_cast<T*>(a.out)[idx] = from_float<T>(v);
                 else if (EPI == EPI_STORE32) static_cast<float*>(a.out)[idx] = v;
+                else if (grp == int(blockIdx.x)) static_cast<float*>(a.out)[idx] = prev + v;
                 else                         static_cast<float*>(a.out)[idx] += v;
             }
         }
