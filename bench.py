@@ -642,16 +642,20 @@ def measure(wl, args, ctx):
     #     to back between two events, alternating between two input buffers so that no launch finds
     #     its input in L2 -- the kernel's own average launch duration.
     ncase = len(wl.cases)
-    isteps = max(1, min(args.steps, 10))
-    events = [torch.cuda.Event(enable_timing=True)]
-    events[0].record()
-    for _ in range(isteps):
-        wl.step(events)
-    barrier()
-    per = [0.0] * ncase
-    for s_ in range(isteps):
-        for i in range(ncase):
-            per[i] += events[s_ * ncase + i].elapsed_time(events[s_ * ncase + i + 1])
+    if ncase == 1:
+        # one kernel per step: its average launch duration over the timed region itself
+        isteps, per = 1, [ms_per_step]
+    else:
+        isteps = max(1, min(args.steps, 10))
+        events = [torch.cuda.Event(enable_timing=True)]
+        events[0].record()
+        for _ in range(isteps):
+            wl.step(events)
+        barrier()
+        per = [0.0] * ncase
+        for s_ in range(isteps):
+            for i in range(ncase):
+                per[i] += events[s_ * ncase + i].elapsed_time(events[s_ * ncase + i + 1])
     alone = None
     if hasattr(wl, "launch_case"):
         reps, alone = 20, []
@@ -681,7 +685,7 @@ def measure(wl, args, ctx):
                 "achieved": kernels[dom][wl.unit], "peak": peak, "unit": wl.unit, "frac": kernels[dom]["frac"],
                 "peak_source": f"{peaks['source']} " + ("cuBLAS bf16 burst" if tensor_bound else "copy bandwidth"),
                 "timing": ("CUDA events around 20 back-to-back launches of this kernel on alternating input buffers"
-                           if alone is not None else "CUDA events around every launch of the step"),
+                           if alone is not None else "CUDA events around the timed region / launches in it"),
                 "traffic": TRAFFIC.get(kernels[dom]["kernel"])}
 
     # ---- end to end: host buffers in, host results out, every step ----------------------
