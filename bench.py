@@ -801,6 +801,8 @@ def _seg_traffic():
             t[f"reduce_{op}<{kind}>"] = (1 << 26) * size + 3 * (1 << 20) * size
         # profiles/segscan_f64_sum_2p25.md: read 1.00x; 78 % of the output reached DRAM before the launch ended
         t[f"scan_inclusive_sum<{kind}>"] = int((1 << 26) * size * (1.0 + 0.784))
+    for kind in ("f16", "bf16"):                                  # profiles/segscan_lane_16bit_sum_2p26.md: 215 MB of 268 MB
+        t[f"scan_inclusive_sum<{kind}>"] = 215_000_000
     return t
 
 
