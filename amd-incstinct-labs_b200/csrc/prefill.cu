@@ -44,6 +44,24 @@ namespace b200p {
 // every launcher on its stream), polled by the bounded waits so that one failed wait ends the launch.
 __device__ int g_device_status[2] = {0, 0};
 
+// Work counters of the persistent prefill kernel: each launch takes the next slot (cleared on its stream
+// before the kernel), so launches in flight on different streams do not share one.
+constexpr unsigned kWorkSlots = 1024;
+__device__ int g_prefill_work[kWorkSlots];
+
+static int* prefill_work_slot() {
+    static int* base[64] = {};
+    static std::atomic<unsigned> next{0};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return nullptr; }
+    if (!base[dev]) {
+        void* ptr = nullptr;
+        if (cudaGetSymbolAddress(&ptr, g_prefill_work) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+        base[dev] = static_cast<int*>(ptr);
+    }
+    return base[dev] + next.fetch_add(1, std::memory_order_relaxed) % kWorkSlots;
+}
+
 int* device_status_ptr() {
     static int* ptrs[64] = {};
     int dev = -1;
@@ -67,7 +85,14 @@ constexpr float kLazyRescale = 8.0f;     // log2 units
 #ifndef B200P_POLY_EVERY
 #define B200P_POLY_EVERY 0
 #endif
-constexpr int kPolyEvery = B200P_POLY_EVERY;   // 0: all exponentials on the SFU; n: one pair in n on the FMA pipes
+constexpr int kPolyEvery = B200P_POLY_EVERY;
+// Tuning aid, compiled in with -DB200P_PREFILL_TIMELINE: clock64 stamps of the first work item's steps go to
+// the debug buffer (knob prefill_variant bit 8).  Off by default: the stamps cost registers in every role.
+#ifdef B200P_PREFILL_TIMELINE
+constexpr bool kTimeline = true;
+#else
+constexpr bool kTimeline = false;
+#endif   // 0: all exponentials on the SFU; n: one pair in n on the FMA pipes
 
 template <int D> struct PrefillShape {
     static constexpr int SUB = D / 64;                         // 64-element boxes per row
@@ -88,6 +113,7 @@ struct PrefillParams {
     float* debug_s;            // optional: raw S of tile (0,0) of CTA (0,0,0), [128][128] fp32
     int* status;               // the library's device status word: raised by a wait that gave up, polled by all waits
     long long* timeline;       // optional (tuning aid): clock64 stamps of CTA (0,0,0), 16 slots per KV tile
+    int* work_counter;         // zero at launch: the CTAs draw the ids of their later work items from it
     int seqQ, seqK, nQH, nKVH, group, batch, causal;
     float scale_log2;
 };
@@ -95,6 +121,32 @@ struct PrefillParams {
 template <typename T> struct Fmt;
 template <> struct Fmt<__half>        { static constexpr int id = 0; };
 template <> struct Fmt<__nv_bfloat16> { static constexpr int id = 1; };
+
+// One work item: 256 query rows (two 128-row tiles) of one (batch, head).  Items are numbered like the
+// blocks of a (query block, head, batch) grid with the query block fastest and the heaviest (latest)
+// query block first, so that items in flight at the same time share their (batch, KV head) in L2.
+struct PrefillItem {
+    int head, b, kvh, nmax;
+    int q0[2], n[2];
+};
+__device__ __forceinline__ PrefillItem prefill_item(const PrefillParams& p, int id) {
+    PrefillItem w;
+    const int nqb = (p.seqQ + 2 * kBM - 1) / (2 * kBM);
+    const int qb = nqb - 1 - id % nqb;
+    w.head = (id / nqb) % p.nQH;
+    w.b = id / (nqb * p.nQH);
+    w.kvh = w.head / p.group;
+    const int ntk = (p.seqK + kBN - 1) / kBN;
+    #pragma unroll
+    for (int t = 0; t < 2; ++t) {
+        w.q0[t] = qb * 2 * kBM + t * kBM;
+        if (w.q0[t] >= p.seqQ) w.n[t] = 0;
+        else if (p.causal) w.n[t] = min(ntk, (w.q0[t] + kBM - 1) / kBN + 1);
+        else w.n[t] = ntk;
+    }
+    w.nmax = max(w.n[0], w.n[1]);
+    return w;
+}
 
 template <typename T, int D, int RS>
 __global__ void __launch_bounds__(prefill_threads(RS), 1)
@@ -112,32 +164,30 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     uint64_t* s_full  = v_empty + VST;        // [2]
     uint64_t* p_half  = s_full + 2;           // [2 tiles][2 halves of P]
     uint64_t* o_done  = p_half + 4;           // [2]
+    uint64_t* q_empty = o_done + 2;           // [1] the item's last Q.K^T has completed: Q may be overwritten
+    uint64_t* o_free  = q_empty + 1;          // [2] the tile's epilogue has read O out of tensor memory
+    uint64_t* item_full  = o_free + 2;        // [2] ring of work-item ids
+    uint64_t* item_empty = item_full + 2;     // [2]
     __shared__ uint32_t s_tmem_base;
     __shared__ int s_failed;
+    __shared__ int s_item[2];
 
     constexpr int kMmaWarp = 8 * RS, kTmaWarp = 8 * RS + 1;
+    constexpr int kItemReaders = 2 * kBM + 1;                  // every softmax thread + the MMA thread
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int nqb = (p.seqQ + 2 * kBM - 1) / (2 * kBM);
-    const int qb = nqb - 1 - int(blockIdx.x);                  // heaviest (latest) query blocks first
-    const int head = blockIdx.y, b = blockIdx.z;
-    const int kvh = head / p.group;
-    const int ntk = (p.seqK + kBN - 1) / kBN;
-    int q0[2], n[2];
-    #pragma unroll
-    for (int t = 0; t < 2; ++t) {
-        q0[t] = qb * 2 * kBM + t * kBM;
-        if (q0[t] >= p.seqQ) n[t] = 0;
-        else if (p.causal) n[t] = min(ntk, (q0[t] + kBM - 1) / kBN + 1);
-        else n[t] = ntk;
-    }
-    const int nmax = max(n[0], n[1]);
+    const int total_items = nqb * p.nQH * p.batch;
 
     if (threadIdx.x == 0) {
         s_failed = 0;
-        dme::mbar_init(q_full, 1);
+        dme::mbar_init(q_full, 1); dme::mbar_init(q_empty, 1);
         for (int s = 0; s < KST; ++s) { dme::mbar_init(&k_full[s], 1); dme::mbar_init(&k_empty[s], 1); }
         for (int s = 0; s < VST; ++s) { dme::mbar_init(&v_full[s], 1); dme::mbar_init(&v_empty[s], 1); }
-        for (int t = 0; t < 2; ++t) { dme::mbar_init(&s_full[t], 1); dme::mbar_init(&p_half[2 * t], kBM); dme::mbar_init(&p_half[2 * t + 1], kBM); dme::mbar_init(&o_done[t], 1); }
+        for (int t = 0; t < 2; ++t) {
+            dme::mbar_init(&s_full[t], 1); dme::mbar_init(&p_half[2 * t], kBM); dme::mbar_init(&p_half[2 * t + 1], kBM);
+            dme::mbar_init(&o_done[t], 1); dme::mbar_init(&o_free[t], kBM);
+            dme::mbar_init(&item_full[t], 1); dme::mbar_init(&item_empty[t], kItemReaders);
+        }
         dme::mbar_init_fence();
     }
     if (warp == kMmaWarp) { tc::tmem_alloc(&s_tmem_base, 512); tc::tmem_relinquish(); }
@@ -146,6 +196,18 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     tc::fence_after_sync();
     const uint32_t tmem = s_tmem_base;
     const uint32_t sm_q = dme::smem_addr(smem + Sh::OFF_Q), sm_k = dme::smem_addr(smem + Sh::OFF_K), sm_v = dme::smem_addr(smem + Sh::OFF_V);
+
+    // The CTA is persistent: it works through items until the launch's counter runs out.  The TMA thread
+    // draws the ids (its own block index first, then gridDim.x + a device-wide atomic counter, i.e. the
+    // order a hardware block scheduler would have used) and publishes them through a two-slot ring; the
+    // other roles read them there.  All barrier phases run on across items, so the next item's Q, K_0 and
+    // first Q.K^T are under way while the softmax warps still normalise and store the previous item's O.
+    auto next_item = [&](int it) -> int {                      // consumer side: id of the CTA's it-th item, or -1
+        if (!dme::wait(&item_full[it & 1], uint32_t((it >> 1) & 1), p.status)) return -2;
+        const int id = *reinterpret_cast<volatile int*>(&s_item[it & 1]);
+        dme::mbar_arrive(&item_empty[it & 1]);
+        return id;
+    };
 
     // Register budget: the softmax warpgroups hold a whole 128-column score row per thread, the
     // MMA / TMA warpgroup needs very little; the three limits must sum to no more than 3 x 168 = 504 (the launch allocation): 216 + 216 + 72.
@@ -156,23 +218,38 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
         // ---------------------------------- TMA producer ----------------------------------
         if (lane == 0) {
             dme::prefetch_tensor_map(&mapQ); dme::prefetch_tensor_map(&mapK); dme::prefetch_tensor_map(&mapV);
-            dme::mbar_arrive_expect_tx(q_full, uint32_t((n[0] > 0) + (n[1] > 0)) * Sh::TILE_BYTES);
-            for (int t = 0; t < 2; ++t) if (n[t] > 0)
-                for (int sb = 0; sb < Sh::SUB; ++sb)
-                    dme::copy_tile_4d(smem + Sh::OFF_Q + t * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapQ, sb * 64, q0[t], head, b, q_full);
             dme::Ring<KST> kr; dme::Ring<VST> vr;
-            for (int j = 0; j < nmax; ++j) {
-                if (j >= KST && !dme::wait(&k_empty[kr.stage], kr.phase ^ 1u, p.status)) { atomicExch(&s_failed, 1); break; }
-                dme::mbar_arrive_expect_tx(&k_full[kr.stage], Sh::TILE_BYTES);
-                for (int sb = 0; sb < Sh::SUB; ++sb)
-                    dme::copy_tile_4d(smem + Sh::OFF_K + kr.stage * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapK, sb * 64, j * kBN, kvh, b, &k_full[kr.stage]);
-                kr.advance();
-                if (j >= VST && !dme::wait(&v_empty[vr.stage], vr.phase ^ 1u, p.status)) { atomicExch(&s_failed, 1); break; }
-                dme::mbar_arrive_expect_tx(&v_full[vr.stage], Sh::TILE_BYTES);
-                for (int sb = 0; sb < Sh::SUB; ++sb)
-                    dme::copy_tile_4d(smem + Sh::OFF_V + vr.stage * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapV, sb * 64, j * kBN, kvh, b, &v_full[vr.stage]);
-                vr.advance();
+            int kloads = 0, vloads = 0;
+            bool ok = true;
+            for (int it = 0; ok; ++it) {
+                // draw and publish the item
+                if (it >= 2 && !dme::wait(&item_empty[it & 1], uint32_t(((it >> 1) - 1) & 1), p.status)) { ok = false; break; }
+                int id = it == 0 ? int(blockIdx.x) : int(gridDim.x) + atomicAdd(p.work_counter, 1);
+                if (id >= total_items) id = -1;
+                s_item[it & 1] = id;
+                dme::mbar_arrive(&item_full[it & 1]);
+                if (id < 0) break;
+                const PrefillItem w = prefill_item(p, id);
+                // Q: the previous item's last Q.K^T must be done with the buffer
+                if (it >= 1 && !dme::wait(q_empty, uint32_t((it - 1) & 1), p.status)) { ok = false; break; }
+                dme::mbar_arrive_expect_tx(q_full, uint32_t((w.n[0] > 0) + (w.n[1] > 0)) * Sh::TILE_BYTES);
+                for (int t = 0; t < 2; ++t) if (w.n[t] > 0)
+                    for (int sb = 0; sb < Sh::SUB; ++sb)
+                        dme::copy_tile_4d(smem + Sh::OFF_Q + t * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapQ, sb * 64, w.q0[t], w.head, w.b, q_full);
+                for (int j = 0; j < w.nmax; ++j) {
+                    if (kloads >= KST && !dme::wait(&k_empty[kr.stage], kr.phase ^ 1u, p.status)) { ok = false; break; }
+                    dme::mbar_arrive_expect_tx(&k_full[kr.stage], Sh::TILE_BYTES);
+                    for (int sb = 0; sb < Sh::SUB; ++sb)
+                        dme::copy_tile_4d(smem + Sh::OFF_K + kr.stage * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapK, sb * 64, j * kBN, w.kvh, w.b, &k_full[kr.stage]);
+                    kr.advance(); ++kloads;
+                    if (vloads >= VST && !dme::wait(&v_empty[vr.stage], vr.phase ^ 1u, p.status)) { ok = false; break; }
+                    dme::mbar_arrive_expect_tx(&v_full[vr.stage], Sh::TILE_BYTES);
+                    for (int sb = 0; sb < Sh::SUB; ++sb)
+                        dme::copy_tile_4d(smem + Sh::OFF_V + vr.stage * Sh::TILE_BYTES + sb * Sh::SUB_BYTES, &mapV, sb * 64, j * kBN, w.kvh, w.b, &v_full[vr.stage]);
+                    vr.advance(); ++vloads;
+                }
             }
+            if (!ok) atomicExch(&s_failed, 1);
         }
       } else if (warp == kMmaWarp) {
         // ---------------------------------- MMA issuer ------------------------------------
@@ -201,40 +278,59 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                     tc::mma_ts(tmem + 256 + t * 128, tmem + t * kBN + kk * 8, vd + uint64_t(kk * (2048 >> 4)),
                                idesc_pv, !(first && kk == 0));
             };
-            bool ok = dme::wait(q_full, 0, p.status);
             dme::Ring<KST> kr; dme::Ring<VST> vr;
-            if (ok && nmax > 0) {
-                ok = dme::wait(&k_full[kr.stage], kr.phase, p.status);
-                tc::fence_after_sync();
-                if (ok) {
-                    for (int t = 0; t < 2; ++t) if (n[t] > 0) { issue_qk(t, kr.stage); tc::commit(&s_full[t]); }
-                    tc::commit(&k_empty[kr.stage]);
-                    kr.advance();
-                }
-            }
-            for (int j = 0; j < nmax && ok; ++j) {
-                ok = dme::wait(&v_full[vr.stage], vr.phase, p.status);
-                if (ok && j + 1 < nmax) ok = dme::wait(&k_full[kr.stage], kr.phase, p.status);
+            int cs0 = 0, cs1 = 0;          // steps of tile 0 / 1 in earlier items: phase of s_full / p_half
+            int co0 = 0, co1 = 0;          // earlier items in which the tile had work: phase of o_done / o_free
+            bool ok = true;
+            for (int it = 0; ok; ++it) {
+                const int id = next_item(it);
+                if (id < 0) { ok = id != -2; break; }
+                const PrefillItem w = prefill_item(p, id);
+                const int nmax = w.nmax, n0 = w.n[0], n1 = w.n[1];
+                ok = dme::wait(q_full, uint32_t(it & 1), p.status);
+                if (ok) ok = dme::wait(&k_full[kr.stage], kr.phase, p.status);
                 if (!ok) break;
-                for (int t = 0; t < 2 && ok; ++t) {
-                    if (j >= n[t]) continue;
-                    ok = dme::wait(&p_half[2 * t], uint32_t(j & 1), p.status);
-                    if (!ok) break;
+                tc::fence_after_sync();
+                if (n0 > 0) { issue_qk(0, kr.stage); tc::commit(&s_full[0]); }
+                if (n1 > 0) { issue_qk(1, kr.stage); tc::commit(&s_full[1]); }
+                tc::commit(&k_empty[kr.stage]);
+                kr.advance();
+                if (nmax == 1) tc::commit(q_empty);
+                const bool dbg = kTimeline && p.timeline && id == 0;
+                // one tile's share of step j: P.V over the two halves of P as they arrive, then the next Q.K^T
+                auto tile_step = [&](auto tc_t, int j, int nt, int cst, int cot) -> bool {
+                    constexpr int t = decltype(tc_t)::value;
+                    if (j >= nt) return true;
+                    if (!dme::wait(&p_half[2 * t], uint32_t((cst + j) & 1), p.status)) return false;
+                    // the first P.V of an item overwrites O_t: the previous item's epilogue must have read it
+                    if (j == 0 && cot > 0 && !dme::wait(&o_free[t], uint32_t((cot - 1) & 1), p.status)) return false;
                     tc::fence_after_sync();
-                    const bool stamp = p.timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 64;
+                    const bool stamp = dbg && j < 64;
                     if (stamp) p.timeline[j * 16 + 8 + 2 * t] = clock64();
                     issue_pv(t, vr.stage, j == 0, 0);                 // keys 0..63 while the softmax finishes 64..127
-                    ok = dme::wait(&p_half[2 * t + 1], uint32_t(j & 1), p.status);
-                    if (!ok) break;
+                    if (!dme::wait(&p_half[2 * t + 1], uint32_t((cst + j) & 1), p.status)) return false;
                     tc::fence_after_sync();
                     issue_pv(t, vr.stage, j == 0, kBN / 32);
-                    if (j + 1 < n[t]) { issue_qk(t, kr.stage); tc::commit(&s_full[t]); }
+                    if (j + 1 < nt) { issue_qk(t, kr.stage); tc::commit(&s_full[t]); }
                     else tc::commit(&o_done[t]);
                     if (stamp) p.timeline[j * 16 + 9 + 2 * t] = clock64();
+                    return true;
+                };
+                for (int j = 0; j < nmax && ok; ++j) {
+                    ok = dme::wait(&v_full[vr.stage], vr.phase, p.status);
+                    if (ok && j + 1 < nmax) ok = dme::wait(&k_full[kr.stage], kr.phase, p.status);
+                    if (!ok) break;
+                    ok = tile_step(std::integral_constant<int, 0>{}, j, n0, cs0, co0);
+                    if (ok) ok = tile_step(std::integral_constant<int, 1>{}, j, n1, cs1, co1);
+                    if (!ok) break;
+                    tc::commit(&v_empty[vr.stage]);
+                    vr.advance();
+                    if (j + 1 < nmax) {
+                        tc::commit(&k_empty[kr.stage]); kr.advance();
+                        if (j + 2 == nmax) tc::commit(q_empty);           // that was the item's last Q.K^T
+                    }
                 }
-                tc::commit(&v_empty[vr.stage]);
-                vr.advance();
-                if (j + 1 < nmax) { tc::commit(&k_empty[kr.stage]); kr.advance(); }
+                cs0 += n0; cs1 += n1; co0 += n0 > 0; co1 += n1 > 0;
             }
             if (!ok) atomicExch(&s_failed, 1);
         }
@@ -249,18 +345,25 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
         const int t = warp / (4 * RS);                        // query tile
         const int half = (warp / 4) % RS;                     // column half of this thread
         const int r = (warp % 4) * 32 + lane;                 // row inside the tile = TMEM lane
-        const int row = q0[t] + r;
         const uint32_t lane_base = uint32_t(32 * (warp % 4)) << 16;
         const uint32_t tS = tmem + lane_base + uint32_t(t * kBN);
         const uint32_t tO = tmem + lane_base + 256u + uint32_t(t * 128) + uint32_t(half * OW);
-        float m_used = -INFINITY, l = 0.f;
+        int cs = 0, co = 0;                                    // as in the MMA thread, for this tile
         bool ok = true;
-        for (int j = 0; j < n[t]; ++j) {
-            if (!dme::wait(&s_full[t], uint32_t(j & 1), p.status)) { ok = false; break; }
+        for (int it = 0; ok; ++it) {
+          const int id = next_item(it);
+          if (id < 0) { ok = id != -2; break; }
+          const PrefillItem w = prefill_item(p, id);
+          const int q0t = t ? w.q0[1] : w.q0[0], nt = t ? w.n[1] : w.n[0];     // no arrays indexed at run time
+          const int o_b = w.b, o_head = w.head;
+          const int row = q0t + r;
+          float m_used = -INFINITY, l = 0.f;
+          for (int j = 0; j < nt; ++j) {
+            if (!dme::wait(&s_full[t], uint32_t((cs + j) & 1), p.status)) { ok = false; break; }
             tc::fence_after_sync();
-            const bool stamp = p.timeline && r == 0 && half == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && j < 64;
+            const bool stamp = kTimeline && p.timeline && r == 0 && half == 0 && id == 0 && j < 64;
             if (stamp) p.timeline[j * 16 + 4 * t + 0] = clock64();
-            const bool need_mask = (p.causal && j * kBN + kBN - 1 > q0[t]) || (j * kBN + kBN > p.seqK);
+            const bool need_mask = (p.causal && j * kBN + kBN - 1 > q0t) || (j * kBN + kBN > p.seqK);
             // columns (of this thread's range) <= col_limit are live
             const int col_limit = min(p.causal ? row : 0x7fffffff, p.seqK - 1) - j * kBN - half * CW;
             // ---- this thread's part of the score row into registers (one wait for all loads) ------------
@@ -269,7 +372,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             for (int c = 0; c < CW / 32; ++c) tc::ld_32x32b_x32(tS + half * CW + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
             tc::wait_ld();
             if (stamp) p.timeline[j * 16 + 4 * t + 1] = clock64();
-            if (p.debug_s && j == 0 && t == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0) {
+            if (p.debug_s && j == 0 && t == 0 && id == 0) {
                 #pragma unroll
                 for (int i = 0; i < CW; ++i) p.debug_s[r * kBN + half * CW + i] = __uint_as_float(sv[i]);
             }
@@ -332,31 +435,34 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             }
             l = l * alpha + ((la[0] + la[1]) + (la[2] + la[3]));
             if (stamp) p.timeline[j * 16 + 4 * t + 3] = clock64();
-        }
-        // ---- epilogue: O / l -> 16-bit; a thread writes its OW output columns of its row --------------
-        if (ok && n[t] > 0) {
-            if (dme::wait(&o_done[t], 0, p.status)) {
-                tc::fence_after_sync();
+          }
+          if (!ok) break;
+          // ---- epilogue: O / l -> 16-bit; a thread writes its OW output columns of its row.  O is taken into
+          // registers first and the tile's tensor memory released, so the next item's P.V does not wait for the stores.
+          if (nt > 0) {
+            if (!dme::wait(&o_done[t], uint32_t(co & 1), p.status)) { ok = false; break; }
+            tc::fence_after_sync();
+            uint32_t v[OW];
+            #pragma unroll
+            for (int c = 0; c < OW / 32; ++c) tc::ld_32x32b_x32(tO + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+            tc::wait_ld();
+            tc::fence_before_sync();
+            dme::mbar_arrive(&o_free[t]);
+            if (row < p.seqQ) {
                 const float inv = l > 0.f ? 1.f / l : 1.f;
-                T* orow = static_cast<T*>(p.O) + size_t(b) * p.o_batch + size_t(head) * p.o_head + size_t(row) * p.o_seq + half * OW;
+                T* orow = static_cast<T*>(p.O) + size_t(o_b) * p.o_batch + size_t(o_head) * p.o_head + size_t(row) * p.o_seq + half * OW;
                 #pragma unroll
-                for (int c = 0; c < OW / 32; ++c) {
-                    uint32_t v[32];
-                    tc::ld_32x32b_x32(tO + c * 32, v);
-                    tc::wait_ld();
-                    if (row < p.seqQ) {
-                        #pragma unroll
-                        for (int q4 = 0; q4 < 4; ++q4) {
-                            uint4 w;
-                            w.x = pack2<T>(__uint_as_float(v[q4 * 8 + 0]) * inv, __uint_as_float(v[q4 * 8 + 1]) * inv);
-                            w.y = pack2<T>(__uint_as_float(v[q4 * 8 + 2]) * inv, __uint_as_float(v[q4 * 8 + 3]) * inv);
-                            w.z = pack2<T>(__uint_as_float(v[q4 * 8 + 4]) * inv, __uint_as_float(v[q4 * 8 + 5]) * inv);
-                            w.w = pack2<T>(__uint_as_float(v[q4 * 8 + 6]) * inv, __uint_as_float(v[q4 * 8 + 7]) * inv);
-                            *reinterpret_cast<uint4*>(orow + c * 32 + q4 * 8) = w;
-                        }
-                    }
+                for (int q8 = 0; q8 < OW / 8; ++q8) {
+                    uint4 o4;
+                    o4.x = pack2<T>(__uint_as_float(v[q8 * 8 + 0]) * inv, __uint_as_float(v[q8 * 8 + 1]) * inv);
+                    o4.y = pack2<T>(__uint_as_float(v[q8 * 8 + 2]) * inv, __uint_as_float(v[q8 * 8 + 3]) * inv);
+                    o4.z = pack2<T>(__uint_as_float(v[q8 * 8 + 4]) * inv, __uint_as_float(v[q8 * 8 + 5]) * inv);
+                    o4.w = pack2<T>(__uint_as_float(v[q8 * 8 + 6]) * inv, __uint_as_float(v[q8 * 8 + 7]) * inv);
+                    *reinterpret_cast<uint4*>(orow + q8 * 8) = o4;
                 }
-            } else ok = false;
+            }
+          }
+          cs += nt; co += nt > 0;
         }
         if (!ok) atomicExch(&s_failed, 1);
     }
@@ -405,7 +511,16 @@ int launch_prefill_rs(const void* Q, const void* K, const void* V, void* O, cons
     p.seqQ = c->seqQ; p.seqK = c->seqK; p.nQH = c->nQHeads; p.nKVH = c->nKVHeads; p.group = c->nQHeads / c->nKVHeads;
     p.batch = c->batch; p.causal = c->causal;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(D));
-    dim3 grid((c->seqQ + 2 * kBM - 1) / (2 * kBM), c->nQHeads, c->batch);
+    p.work_counter = prefill_work_slot();
+    if (!p.work_counter) return B200P_E_NO_DEVICE;
+    if (cudaError_t ce = cudaMemsetAsync(p.work_counter, 0, sizeof(int), st)) return int(ce);
+    // One persistent CTA per SM (the kernel takes all of an SM's shared and tensor memory), or one CTA per
+    // work item when the knob's bit 1 is set.
+    const long long items = (long long)((c->seqQ + 2 * kBM - 1) / (2 * kBM)) * c->nQHeads * c->batch;
+    if (items > 0x7fffffffLL / 2) return B200P_E_RANGE;
+    const int sms = sm_count();
+    const bool one_per_item = (tuning(KNOB_PREFILL_VARIANT, 0) & 2) != 0;
+    dim3 grid(unsigned(one_per_item || items < sms ? items : sms), 1, 1);
     kern<<<grid, prefill_threads(RS), Sh::SMEM_BYTES, st>>>(p, mq, mk, mv);
     return launched();
 }
