@@ -10,8 +10,10 @@
 // 16-bit output, O / l with l > 0 guarded.
 //
 // The reference keeps S, P and O in LDS, one 16-row block per wave, and rescales
-// O serially on lane 0.  Here a CTA owns 256 query rows of one (batch, head) as
-// two 128-row tiles and is warp-specialised:
+// O serially on lane 0.  Here a work item is 256 query rows of one (batch, head)
+// as two 128-row tiles; one persistent CTA per SM (it takes all of the SM's shared
+// and tensor memory) draws items from a device-wide counter, heaviest query blocks
+// of a head first, and is warp-specialised:
 //   warp 9        TMA producer: Q once, then K_j / V_j tiles ([128][D], 64-element
 //                 boxes, 128-byte swizzle) into two mbarrier rings;
 //   warp 8        MMA issuer (one thread): S_t = Q_t.K_j^T and O_t += P_t.V_j as
@@ -24,6 +26,10 @@
 //                 no cross-lane step at all), exp2 with the scale folded in, lazy
 //                 rescaling of O (only when the running max grew by more than 2^8),
 //                 final O / l and the store.
+// All barrier phases run on from one item to the next, so the next item's Q, K_0 and
+// first Q.K^T are in flight while the softmax warps normalise and store the previous
+// item's O (measured per item: 18.5k cycles of fill, drain and launch with one CTA per
+// item, 16.5k with persistent CTAs, on top of 3.5k per 128-key step).
 // TMEM columns: S_0 [0,128) S_1 [128,256) O_0 [256,256+D) O_1 [384,384+D).
 // Compute-bound on the bf16 tensor pipe; K/V are re-read from L2 by the CTAs of
 // the same (batch, kv head), which are adjacent in the grid.
