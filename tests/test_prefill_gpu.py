@@ -116,3 +116,53 @@ def test_full_size_config_sampled(b200p, torch_cuda):
     ones = torch.ones_like(V)
     O1 = b200p.prefill(Q, K, ones, causal=True)
     assert (O1.float() - 1.0).abs().max().item() < 1e-2
+
+
+@pytest.mark.parametrize("causal", [1, 0])
+@pytest.mark.parametrize("D", [128, 64])
+def test_more_work_items_than_sms(b200p, torch_cuda, D, causal):
+    """The kernel's CTAs are persistent (one per SM) and draw 256-row work items from a device
+    counter.  Here there are more items than SMs (2 x 20 heads x 5 query blocks = 200), of
+    unequal length under the causal mask, a ragged last block and GQA; every output row against
+    the oracle; the one-CTA-per-item launch (knob bit 1) gives the same bits."""
+    torch = torch_cuda
+    rng = np.random.default_rng(41 + D + causal)
+    batch, nqh, nkvh, sq = 2, 20, 4, 1200
+    q = orc.round_to((rng.standard_normal((batch, nqh, sq, D)) * 0.5).astype(np.float32), "bf16")
+    k = orc.round_to((rng.standard_normal((batch, nkvh, sq, D)) * 0.5).astype(np.float32), "bf16")
+    v = orc.round_to((rng.standard_normal((batch, nkvh, sq, D)) * 0.5).astype(np.float32), "bf16")
+    ref = orc.cpu_prefill(q, k, v, D, sq, sq, nqh, nkvh, batch, causal, threads=8)
+    Q, K, V = dev16(torch, q, "bf16"), dev16(torch, k, "bf16"), dev16(torch, v, "bf16")
+    got = b200p.prefill(Q, K, V, causal=bool(causal))
+    assert b200p.device_status() == 0
+    assert np.abs(got.float().cpu().numpy() - ref).max() < TOL
+    b200p.set_tuning("prefill_variant", 2)
+    try:
+        assert torch.equal(b200p.prefill(Q, K, V, causal=bool(causal)), got)
+    finally:
+        b200p.set_tuning("prefill_variant", -1)
+
+
+def test_launches_on_two_streams_do_not_share_a_work_counter(b200p, torch_cuda):
+    """Two prefill launches in flight at once on different streams each draw their items from
+    their own counter slot: both results equal the single-stream ones."""
+    torch = torch_cuda
+    g = torch.Generator(device="cuda"); g.manual_seed(77)
+    mk = lambda b, h, s: (torch.randn(b, h, s, 128, device="cuda", generator=g) * 0.5).bfloat16()
+    A = [mk(4, 16, 2048) for _ in range(3)]
+    Bq = [mk(2, 24, 1536) for _ in range(3)]
+    ref_a = b200p.prefill(*A, causal=True)
+    ref_b = b200p.prefill(*Bq, causal=True)
+    torch.cuda.synchronize()
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    outs = []
+    for _ in range(3):
+        with torch.cuda.stream(s1):
+            oa = b200p.prefill(*A, causal=True)
+        with torch.cuda.stream(s2):
+            ob = b200p.prefill(*Bq, causal=True)
+        outs.append((oa, ob))
+    torch.cuda.synchronize()
+    for oa, ob in outs:
+        assert torch.equal(oa, ref_a) and torch.equal(ob, ref_b)
+    assert b200p.device_status() == 0
