@@ -72,6 +72,22 @@ template <typename T> int by_vec(int fn, int op, int vec, const void* in, void* 
 }
 } // namespace
 
+// lane_scan_kogge_stone<64>: every lane scans a whole 64-element segment of its own (32 segments per call).
+template <typename Op> void run_lane_scan(const float* in, float* out) {
+    run_warp([=](unsigned l) {
+        float v[64];
+        for (int i = 0; i < 64; ++i) v[i] = in[l * 64 + i];
+        wave::lane_scan_kogge_stone<64>(v, Op{});
+        for (int i = 0; i < 64; ++i) out[l * 64 + i] = v[i];
+    });
+}
+extern "C" int emu_lane_scan(int op, const float* in, float* out) {
+    if (op == 0) run_lane_scan<wave::SumOp>(in, out);
+    else if (op == 1) run_lane_scan<wave::MaxOp>(in, out);
+    else run_lane_scan<wave::MinOp>(in, out);
+    return 0;
+}
+
 // dtype: 0 f32, 1 f64, 2 i32, 3 i64
 extern "C" int emu_run(int fn, int op, int dtype, int vec, const void* in, void* out) {
     if (fn == FN_PAIR_API) return -1;

@@ -89,6 +89,20 @@ def test_kogge_stone_64_is_portable_scan(emu, vec, op):
     assert np.array_equal(got, ref)
 
 
+@pytest.mark.parametrize("kind", ["f16", "bf16"])
+@pytest.mark.parametrize("op", [orc.SUM, orc.MAX, orc.MIN])
+def test_lane_serial_kogge_stone_is_portable_scan(emu, op, kind):
+    """lane_scan_kogge_stone<64> (one lane holds the whole segment, as the 16-bit array scan does)
+    gives the bits of the reference's fp32 Hillis-Steele scan over 64 lanes (wave_scan.hpp:52-74)."""
+    bf = kind == "bf16"
+    x = orc.round_to(data(np.float32, 32 * 64, 90 + op), kind)
+    out = np.empty_like(x)
+    assert emu.emu_lane_scan(op, x.ctypes.data_as(C.c_void_p), out.ctypes.data_as(C.c_void_p)) == 0
+    bits = orc.f32_to_bf16_bits(x) if bf else orc.f32_to_f16_bits(x)
+    got = orc.f32_to_bf16_bits(out) if bf else orc.f32_to_f16_bits(out)
+    assert np.array_equal(got, orc.shfl_scan_narrow(op, bits, bf16=bf))
+
+
 @pytest.mark.parametrize("dt", [np.float32, np.float64, np.int32, np.int64])
 def test_pair_api_known_answers(emu, dt):
     """The public wave::dpp:: pair API on the reference's probe vectors
