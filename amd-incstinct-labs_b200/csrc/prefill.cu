@@ -92,13 +92,9 @@ constexpr float kLazyRescale = 8.0f;     // log2 units
 #define B200P_POLY_EVERY 0
 #endif
 constexpr int kPolyEvery = B200P_POLY_EVERY;
-// Tuning aid, compiled in with -DB200P_PREFILL_TIMELINE: clock64 stamps of the first work item's steps go to
-// the debug buffer (knob prefill_variant bit 8).  Off by default: the stamps cost registers in every role.
-#ifdef B200P_PREFILL_TIMELINE
-constexpr bool kTimeline = true;
-#else
-constexpr bool kTimeline = false;
-#endif   // 0: all exponentials on the SFU; n: one pair in n on the FMA pipes
+// The debug instantiation (DBG, used by b200p_attn_prefill_debug only) can write the raw scores of the first
+// tile or clock64 stamps of the first work item's steps to the debug buffer; the production instantiation carries
+// neither: the stamps alone cost the softmax warps enough registers to spill.   // 0: all exponentials on the SFU; n: one pair in n on the FMA pipes
 
 template <int D> struct PrefillShape {
     static constexpr int SUB = D / 64;                         // 64-element boxes per row
@@ -154,7 +150,7 @@ __device__ __forceinline__ PrefillItem prefill_item(const PrefillParams& p, int 
     return w;
 }
 
-template <typename T, int D, int RS>
+template <typename T, int D, int RS, bool DBG>
 __global__ void __launch_bounds__(prefill_threads(RS), 1)
 prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ,
                   const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
@@ -302,7 +298,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                 tc::commit(&k_empty[kr.stage]);
                 kr.advance();
                 if (nmax == 1) tc::commit(q_empty);
-                const bool dbg = kTimeline && p.timeline && id == 0;
+                const bool dbg = DBG && p.timeline && id == 0;
                 // one tile's share of step j: P.V over the two halves of P as they arrive, then the next Q.K^T
                 auto tile_step = [&](auto tc_t, int j, int nt, int cst, int cot) -> bool {
                     constexpr int t = decltype(tc_t)::value;
@@ -367,7 +363,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
           for (int j = 0; j < nt; ++j) {
             if (!dme::wait(&s_full[t], uint32_t((cs + j) & 1), p.status)) { ok = false; break; }
             tc::fence_after_sync();
-            const bool stamp = kTimeline && p.timeline && r == 0 && half == 0 && id == 0 && j < 64;
+            const bool stamp = DBG && p.timeline && r == 0 && half == 0 && id == 0 && j < 64;
             if (stamp) p.timeline[j * 16 + 4 * t + 0] = clock64();
             const bool need_mask = (p.causal && j * kBN + kBN - 1 > q0t) || (j * kBN + kBN > p.seqK);
             // columns (of this thread's range) <= col_limit are live
@@ -378,7 +374,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             for (int c = 0; c < CW / 32; ++c) tc::ld_32x32b_x32(tS + half * CW + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
             tc::wait_ld();
             if (stamp) p.timeline[j * 16 + 4 * t + 1] = clock64();
-            if (p.debug_s && j == 0 && t == 0 && id == 0) {
+            if (DBG && p.debug_s && j == 0 && t == 0 && id == 0) {
                 #pragma unroll
                 for (int i = 0; i < CW; ++i) p.debug_s[r * kBN + half * CW + i] = __uint_as_float(sv[i]);
             }
@@ -496,13 +492,14 @@ int launch_prefill_rs(const void* Q, const void* K, const void* V, void* O, cons
     if (e == cudaSuccess) e = make_tensor_map(&mv, dt, 4, V, kd, vs, box, Swizzle::B128);
     if (e != cudaSuccess) return int(e);
 
-    auto kern = prefill_tc_kernel<T, D, RS>;
-    static bool attr_set[64] = {};
+    const bool dbg = debug_s != nullptr;
+    auto kern = dbg ? prefill_tc_kernel<T, D, RS, true> : prefill_tc_kernel<T, D, RS, false>;
+    static bool attr_set[64][2] = {};
     int dev = 0; cudaGetDevice(&dev);
-    if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (dev >= 0 && dev < 64 && !attr_set[dev][dbg]) {
         e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Sh::SMEM_BYTES);
         if (e != cudaSuccess) return int(e);
-        attr_set[dev] = true;
+        attr_set[dev][dbg] = true;
     }
     PrefillParams p{};
     p.O = O; p.debug_s = debug_s; p.timeline = nullptr;
