@@ -28,7 +28,8 @@ enum Knob {
     KNOB_RUNTIME_GRAPH,         // 1: the runtime replays its decode step as a CUDA graph, 0: launches it every step
     KNOB_RUNTIME_PDL,           // 1: skinny kernels launch as programmatic dependents (weights prefetched before the wait)
     KNOB_RUNTIME_ROPE_FUSED,    // 1: RoPE + KV scatter in the Q/K/V projection's epilogue, 0: separate kernel
-    KNOB_RUNTIME_SKINNY,        // 1: decode-step projections on skinny_gemm_kernel, 0: library GEMMs
+    KNOB_RUNTIME_SKINNY,        // decode-step projections: 0 library GEMMs, 1 skinny_gemm_kernel (W in registers),
+                                // 2 skinny_stream_kernel (W through shared memory; default)
     KNOB_SCAN16_LANE,           // 1: 16-bit scans hold a whole segment per lane, 0: four lanes per segment
     KNOB_COUNT
 };

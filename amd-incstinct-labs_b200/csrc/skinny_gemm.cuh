@@ -38,6 +38,7 @@
 #pragma once
 #include "common.cuh"
 #include "attn_common.cuh"
+#include "dme/dme_tma.cuh"
 #include "mma_sync.cuh"
 #include "vec_io.cuh"
 #include "wave_primitives/wave64.cuh"
@@ -79,6 +80,145 @@ constexpr int kSkinnyWarps = kSkinnyThreads / 32;
 constexpr int kSkinnyMaxM = 8;
 constexpr int kSkinnyDepth = 4;       // 64-column blocks in flight per warp
 constexpr int kSkinnyXPad = 8;        // elements: X rows are 16 bytes longer than K
+
+// Barrier over the 256 threads that compute (the whole CTA of skinny_gemm_kernel; the eight
+// consumer warps of skinny_stream_kernel, whose producer warp is streaming meanwhile).
+__device__ __forceinline__ void skinny_barrier() { asm volatile("bar.sync 1, %0;" :: "r"(kSkinnyThreads) : "memory"); }
+
+// X into shared memory as 16-bit rows of K + kSkinnyXPad elements, rows in [M, Mp) zero; ends with a barrier.
+template <typename T, int PRO>
+__device__ __forceinline__ void skinny_prologue(const SkinnyArgs& a, T* xs, float* part_ss, int Mp, int warp, int lane) {
+    const int K = a.K, xstride = K + kSkinnyXPad;
+    // ---- prologue: X into shared memory as 16-bit, rows in [M, Mp) zero --------------------------------
+    if (PRO == PRO_RMSNORM) {
+        // forward.hpp:34-56: y = x * rsqrt(mean(x^2) + eps) * w.  8 / Mp warps share a row; each keeps
+        // up to 4 quads per lane in registers between the sum of squares and the scaling.
+        constexpr int CACHE = 4;
+        const int wpr = kSkinnyWarps / Mp;                      // warps per row
+        const int m = warp / wpr, part = warp % wpr;
+        const int quads = K / 4, qper = (quads + wpr - 1) / wpr;
+        const int q0 = part * qper, q1 = min(q0 + qper, quads);
+        const float* x = a.X32 + size_t(m) * K;
+        const T* nw = static_cast<const T*>(a.norm_w);
+        T* dst = xs + size_t(m) * xstride;
+        float4 cx[CACHE]; uint2 cw[CACHE];
+        float ss = 0.f;
+        if (m < a.M) {
+            #pragma unroll
+            for (int it = 0; it < CACHE; ++it) {
+                const int q = q0 + lane + 32 * it;
+                if (q < q1) {
+                    cx[it] = *reinterpret_cast<const float4*>(x + 4 * q);
+                    cw[it] = *reinterpret_cast<const uint2*>(nw + 4 * q);
+                    ss += cx[it].x * cx[it].x + cx[it].y * cx[it].y + cx[it].z * cx[it].z + cx[it].w * cx[it].w;
+                }
+            }
+            for (int q = q0 + lane + 32 * CACHE; q < q1; q += 32) {
+                const float4 v = *reinterpret_cast<const float4*>(x + 4 * q);
+                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+            }
+        }
+        ss = wave::dpp::reduce_sum(ss);
+        if (lane == 0) part_ss[warp] = ss;
+        skinny_barrier();
+        float tot = 0.f;
+        for (int w = 0; w < wpr; ++w) tot += part_ss[m * wpr + w];
+        const float inv = rsqrtf(tot / K + a.eps);
+        auto put = [&](int q, const float4& v, const uint2& wv) {
+            const T* w4 = reinterpret_cast<const T*>(&wv);
+            uint2 o;
+            o.x = pack2<T>(v.x * inv * to_float(w4[0]), v.y * inv * to_float(w4[1]));
+            o.y = pack2<T>(v.z * inv * to_float(w4[2]), v.w * inv * to_float(w4[3]));
+            *reinterpret_cast<uint2*>(dst + 4 * q) = o;
+        };
+        if (m < a.M) {
+            #pragma unroll
+            for (int it = 0; it < CACHE; ++it) {
+                const int q = q0 + lane + 32 * it;
+                if (q < q1) put(q, cx[it], cw[it]);
+            }
+            for (int q = q0 + lane + 32 * CACHE; q < q1; q += 32)
+                put(q, *reinterpret_cast<const float4*>(x + 4 * q), *reinterpret_cast<const uint2*>(nw + 4 * q));
+        } else {
+            for (int q = q0 + lane; q < q1; q += 32) *reinterpret_cast<uint2*>(dst + 4 * q) = make_uint2(0u, 0u);
+        }
+    } else {
+        const int vec_per_row = K / 8;                          // 16-byte vectors
+        for (int i = (warp * 32 + lane); i < Mp * vec_per_row; i += kSkinnyThreads) {
+            const int m = i / vec_per_row, v = i % vec_per_row;
+            uint4 val = make_uint4(0u, 0u, 0u, 0u);
+            if (m < a.M) val = *reinterpret_cast<const uint4*>(static_cast<const T*>(a.X16) + size_t(m) * a.ldx + size_t(v) * 8);
+            *reinterpret_cast<uint4*>(xs + size_t(m) * xstride + size_t(v) * 8) = val;
+        }
+    }
+    skinny_barrier();
+
+}
+
+// The eight warps' partial accumulators (red[warp][lane][4]: the m16n8 C fragments) meet; the first 64 * R
+// threads write the group's outputs.  prev: for EPI_ACC32, the residual values fetched ahead (use_prev).
+template <typename T, int EPI, int R>
+__device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, const float (*red)[32][4], int grp, int tid, bool use_prev, float prev) {
+        if (EPI == EPI_SILU16) {
+            if (tid < 64) {
+                const int l = tid % 32, sel = tid / 32;
+                float gate = 0.f, up = 0.f;
+                #pragma unroll
+                for (int w = 0; w < kSkinnyWarps; ++w) { gate += red[w][l][sel]; up += red[w][l][2 + sel]; }
+                const int m = 2 * (l % 4) + sel, p = grp * 8 + l / 4;
+                if (m < a.M && p < a.N)
+                    static_cast<T*>(a.out)[size_t(m) * a.ldo + p] = from_float<T>((gate / (1.f + expf(-gate))) * up);
+            }
+        } else if (EPI == EPI_ROPE) {
+            if (tid < 64) {
+                const SkinnyRope& r = a.rope;
+                const int l = tid % 32, sel = tid / 32;
+                float x0 = 0.f, x1 = 0.f;
+                #pragma unroll
+                for (int w = 0; w < kSkinnyWarps; ++w) { x0 += red[w][l][sel]; x1 += red[w][l][2 + sel]; }
+                const int m = 2 * (l % 4) + sel;
+                if (m < a.M) {
+                    const int cph = r.D / 16, half = r.D / 2;
+                    const int slot = grp / cph, d = (grp % cph) * 8 + l / 4;
+                    x0 = to_float(from_float<T>(x0)); x1 = to_float(from_float<T>(x1));      // the projection's 16-bit output
+                    if (r.bias) {
+                        const T* bias = static_cast<const T*>(r.bias);
+                        x0 = to_float(from_float<T>(x0 + to_float(bias[slot * r.D + d])));
+                        x1 = to_float(from_float<T>(x1 + to_float(bias[slot * r.D + d + half])));
+                    }
+                    const int pos = r.pos_dev ? min(*r.pos_dev, r.max_seq - 1) : r.pos0;
+                    if (slot < r.nQH + r.nKVH) {                  // q or k: rotate
+                        const float c = r.cos_t[size_t(pos) * half + d], sn = r.sin_t[size_t(pos) * half + d];
+                        const float y0 = x0 * c - x1 * sn, y1 = x1 * c + x0 * sn;
+                        x0 = y0; x1 = y1;
+                    }
+                    const T o0 = from_float<T>(x0), o1 = from_float<T>(x1);
+                    if (slot < r.nQH) {                           // q stays in the token-major buffer
+                        T* row = static_cast<T*>(a.out) + size_t(m) * a.ldo + size_t(slot) * r.D;
+                        row[d] = o0; row[d + half] = o1;
+                    } else {                                      // k or v: into cache[m][kvh][pos][:]
+                        const bool is_k = slot < r.nQH + r.nKVH;
+                        const int kvh = is_k ? slot - r.nQH : slot - r.nQH - r.nKVH;
+                        T* dst = static_cast<T*>(is_k ? r.kcache : r.vcache) + ((size_t(m) * r.nKVH + kvh) * r.max_seq + pos) * r.D;
+                        dst[d] = o0; dst[d + half] = o1;
+                    }
+                }
+            }
+        } else if (tid < 64 * R) {
+            const int l = tid % 32, c = tid / 32;
+            float v = 0.f;
+            #pragma unroll
+            for (int w = 0; w < kSkinnyWarps; ++w) v += red[w][l][c];
+            const int m = 2 * (l % 4) + (c & 1), n = grp * 8 * R + l / 4 + 8 * (c >> 1);
+            if (m < a.M && n < a.N) {
+                const size_t idx = size_t(m) * a.ldo + n;
+                if (EPI == EPI_STORE16)      static_cast<T*>(a.out)[idx] = from_float<T>(v);
+                else if (EPI == EPI_STORE32) static_cast<float*>(a.out)[idx] = v;
+                else if (use_prev) static_cast<float*>(a.out)[idx] = prev + v;
+                else                         static_cast<float*>(a.out)[idx] += v;
+            }
+        }
+}
 
 // R = rows of W per lane: 2 -> a CTA step covers 16 rows (accumulator rows g and g + 8), 4 column
 // blocks in flight; 1 -> 8 rows (the upper half of the A operand is zero), 8 blocks in flight: twice
@@ -151,69 +291,7 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     // Everything below reads what earlier kernels of the stream produced.
     griddep_wait();
 
-    // ---- prologue: X into shared memory as 16-bit, rows in [M, Mp) zero --------------------------------
-    if (PRO == PRO_RMSNORM) {
-        // forward.hpp:34-56: y = x * rsqrt(mean(x^2) + eps) * w.  8 / Mp warps share a row; each keeps
-        // up to 4 quads per lane in registers between the sum of squares and the scaling.
-        constexpr int CACHE = 4;
-        const int wpr = kSkinnyWarps / Mp;                      // warps per row
-        const int m = warp / wpr, part = warp % wpr;
-        const int quads = K / 4, qper = (quads + wpr - 1) / wpr;
-        const int q0 = part * qper, q1 = min(q0 + qper, quads);
-        const float* x = a.X32 + size_t(m) * K;
-        const T* nw = static_cast<const T*>(a.norm_w);
-        T* dst = xs + size_t(m) * xstride;
-        float4 cx[CACHE]; uint2 cw[CACHE];
-        float ss = 0.f;
-        if (m < a.M) {
-            #pragma unroll
-            for (int it = 0; it < CACHE; ++it) {
-                const int q = q0 + lane + 32 * it;
-                if (q < q1) {
-                    cx[it] = *reinterpret_cast<const float4*>(x + 4 * q);
-                    cw[it] = *reinterpret_cast<const uint2*>(nw + 4 * q);
-                    ss += cx[it].x * cx[it].x + cx[it].y * cx[it].y + cx[it].z * cx[it].z + cx[it].w * cx[it].w;
-                }
-            }
-            for (int q = q0 + lane + 32 * CACHE; q < q1; q += 32) {
-                const float4 v = *reinterpret_cast<const float4*>(x + 4 * q);
-                ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-            }
-        }
-        ss = wave::dpp::reduce_sum(ss);
-        if (lane == 0) part_ss[warp] = ss;
-        __syncthreads();
-        float tot = 0.f;
-        for (int w = 0; w < wpr; ++w) tot += part_ss[m * wpr + w];
-        const float inv = rsqrtf(tot / K + a.eps);
-        auto put = [&](int q, const float4& v, const uint2& wv) {
-            const T* w4 = reinterpret_cast<const T*>(&wv);
-            uint2 o;
-            o.x = pack2<T>(v.x * inv * to_float(w4[0]), v.y * inv * to_float(w4[1]));
-            o.y = pack2<T>(v.z * inv * to_float(w4[2]), v.w * inv * to_float(w4[3]));
-            *reinterpret_cast<uint2*>(dst + 4 * q) = o;
-        };
-        if (m < a.M) {
-            #pragma unroll
-            for (int it = 0; it < CACHE; ++it) {
-                const int q = q0 + lane + 32 * it;
-                if (q < q1) put(q, cx[it], cw[it]);
-            }
-            for (int q = q0 + lane + 32 * CACHE; q < q1; q += 32)
-                put(q, *reinterpret_cast<const float4*>(x + 4 * q), *reinterpret_cast<const uint2*>(nw + 4 * q));
-        } else {
-            for (int q = q0 + lane; q < q1; q += 32) *reinterpret_cast<uint2*>(dst + 4 * q) = make_uint2(0u, 0u);
-        }
-    } else {
-        const int vec_per_row = K / 8;                          // 16-byte vectors
-        for (int i = threadIdx.x; i < Mp * vec_per_row; i += kSkinnyThreads) {
-            const int m = i / vec_per_row, v = i % vec_per_row;
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (m < a.M) val = *reinterpret_cast<const uint4*>(static_cast<const T*>(a.X16) + size_t(m) * a.ldx + size_t(v) * 8);
-            *reinterpret_cast<uint4*>(xs + size_t(m) * xstride + size_t(v) * 8) = val;
-        }
-    }
-    __syncthreads();
+    skinny_prologue<T, PRO>(a, xs, part_ss, Mp, warp, lane);
 
     // EPI_ACC32: fetch the first group's residual values now, so the epilogue's read-modify-write
     // does not start with a trip to L2
@@ -256,66 +334,131 @@ skinny_gemm_kernel(const SkinnyArgs a) {
 
         // ---- the 8 warps' partial sums meet; epilogue (the next group's loads are in flight) ---------
         *reinterpret_cast<float4*>(&red[parity][warp][lane][0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
-        __syncthreads();
-        if (EPI == EPI_SILU16) {
-            if (threadIdx.x < 64) {
-                const int l = threadIdx.x % 32, sel = threadIdx.x / 32;
-                float gate = 0.f, up = 0.f;
-                #pragma unroll
-                for (int w = 0; w < kSkinnyWarps; ++w) { gate += red[parity][w][l][sel]; up += red[parity][w][l][2 + sel]; }
-                const int m = 2 * (l % 4) + sel, p = grp * 8 + l / 4;
-                if (m < a.M && p < a.N)
-                    static_cast<T*>(a.out)[size_t(m) * a.ldo + p] = from_float<T>((gate / (1.f + expf(-gate))) * up);
-            }
-        } else if (EPI == EPI_ROPE) {
-            if (threadIdx.x < 64) {
-                const SkinnyRope& r = a.rope;
-                const int l = threadIdx.x % 32, sel = threadIdx.x / 32;
-                float x0 = 0.f, x1 = 0.f;
-                #pragma unroll
-                for (int w = 0; w < kSkinnyWarps; ++w) { x0 += red[parity][w][l][sel]; x1 += red[parity][w][l][2 + sel]; }
-                const int m = 2 * (l % 4) + sel;
-                if (m < a.M) {
-                    const int cph = r.D / 16, half = r.D / 2;
-                    const int slot = grp / cph, d = (grp % cph) * 8 + l / 4;
-                    x0 = to_float(from_float<T>(x0)); x1 = to_float(from_float<T>(x1));      // the projection's 16-bit output
-                    if (r.bias) {
-                        const T* bias = static_cast<const T*>(r.bias);
-                        x0 = to_float(from_float<T>(x0 + to_float(bias[slot * r.D + d])));
-                        x1 = to_float(from_float<T>(x1 + to_float(bias[slot * r.D + d + half])));
+        skinny_barrier();
+        skinny_epilogue<T, EPI, R>(a, red[parity], grp, threadIdx.x, grp == int(blockIdx.x), prev);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// skinny_stream_kernel: the same product with W staged through shared memory.
+// In skinny_gemm_kernel the bytes in flight are the registers that hold them
+// (8 KB per warp), and a group's loads are only issued once the previous group has
+// been consumed.  Here a producer thread streams W with bulk copies into a ring of
+// shared-memory stages (16 rows x up to 2048 columns each, ~64 KB, as many as fit
+// beside X), running as far ahead of the eight consumer warps as the ring allows,
+// across row groups; one persistent CTA per SM.  Rows are 16 bytes longer than the
+// slab so that the 16-byte fragment reads of a quarter-warp (two rows x four column
+// chunks) fall on eight different bank groups.  The consumers read their A
+// fragments from the stage exactly as skinny_gemm_kernel reads them from
+// registers; prologue and epilogue are shared.  Waits are bounded; a wait that
+// gives up raises *status and the kernel drains.
+// ---------------------------------------------------------------------------
+constexpr int kSkinnySlab = 2048;                  // columns of W per stage
+constexpr int kSkinnyStreamThreads = kSkinnyThreads + 32;
+
+template <typename T, int PRO, int EPI>
+__global__ void __launch_bounds__(kSkinnyStreamThreads, 1)
+skinny_stream_kernel(const SkinnyArgs a, int nstages, int slab_cols, int* status) {
+    griddep_launch_dependents();
+    extern __shared__ __align__(128) unsigned char skinny_smem[];
+    __shared__ float red[2][kSkinnyWarps][32][4];
+    __shared__ float part_ss[kSkinnyWarps];
+    __shared__ uint64_t bars[16];
+    constexpr int kMaxStages = 8;
+    uint64_t* full_bar = bars;
+    uint64_t* empty_bar = bars + kMaxStages;
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int K = a.K, xstride = K + kSkinnyXPad;
+    const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
+    const int slab = K < slab_cols ? K : slab_cols;               // columns per stage
+    const int nslab = (K + slab - 1) / slab;
+    const int rowb = slab * 2 + 16;                               // bytes between rows of a stage
+    const int stage_bytes = 16 * rowb;
+    const int x_bytes = ((Mp * xstride * 2 + 127) / 128) * 128;
+    T* xs = reinterpret_cast<T*>(skinny_smem);
+    unsigned char* stages = skinny_smem + x_bytes;
+    const int ngroups = (EPI == EPI_SILU16) ? (a.N + 7) / 8 : (a.N + 15) / 16;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < nstages; ++s) { dme::mbar_init(&full_bar[s], 1); dme::mbar_init(&empty_bar[s], kSkinnyWarps); }
+        dme::mbar_init_fence();
+    }
+    __syncthreads();
+
+    if (warp == kSkinnyWarps) {
+        // ---- producer: W is constant, so it streams before and through the dependency wait of the consumers ----
+        if (lane == 0) {
+            const uint64_t pol = dme::policy_evict_first();
+            int stage = 0, uses = 0; uint32_t phase = 0;
+            bool ok = true;
+            for (int grp = blockIdx.x; grp < ngroups && ok; grp += gridDim.x) {
+                for (int sl = 0; sl < nslab; ++sl) {
+                    if (uses >= nstages && !dme::wait(&empty_bar[stage], phase ^ 1u, status)) { ok = false; break; }
+                    const int c0 = sl * slab, cols = min(slab, K - c0);
+                    unsigned char* dst = stages + size_t(stage) * stage_bytes;
+                    dme::mbar_arrive_expect_tx(&full_bar[stage], uint32_t(16 * cols * 2));
+                    for (int r = 0; r < 16; ++r) {
+                        size_t row;
+                        if (EPI == EPI_SILU16)    row = r < 8 ? size_t(min(grp * 8 + r, a.N - 1)) : size_t(a.N) + size_t(min(grp * 8 + r - 8, a.N - 1));
+                        else if (EPI == EPI_ROPE) { const int cph = a.rope.D / 16;
+                                                    row = size_t(grp / cph) * a.rope.D + size_t(grp % cph) * 8 + (r & 7) + (r >= 8 ? a.rope.D / 2 : 0); }
+                        else                      row = size_t(min(grp * 16 + r, a.N - 1));
+                        dme::copy_tile_1d_stream(dst + size_t(r) * rowb, static_cast<const char*>(a.W) + (row * size_t(K) + c0) * 2,
+                                                 uint32_t(cols * 2), &full_bar[stage], pol);
                     }
-                    const int pos = r.pos_dev ? min(*r.pos_dev, r.max_seq - 1) : r.pos0;
-                    if (slot < r.nQH + r.nKVH) {                  // q or k: rotate
-                        const float c = r.cos_t[size_t(pos) * half + d], sn = r.sin_t[size_t(pos) * half + d];
-                        const float y0 = x0 * c - x1 * sn, y1 = x1 * c + x0 * sn;
-                        x0 = y0; x1 = y1;
-                    }
-                    const T o0 = from_float<T>(x0), o1 = from_float<T>(x1);
-                    if (slot < r.nQH) {                           // q stays in the token-major buffer
-                        T* row = static_cast<T*>(a.out) + size_t(m) * a.ldo + size_t(slot) * r.D;
-                        row[d] = o0; row[d + half] = o1;
-                    } else {                                      // k or v: into cache[m][kvh][pos][:]
-                        const bool is_k = slot < r.nQH + r.nKVH;
-                        const int kvh = is_k ? slot - r.nQH : slot - r.nQH - r.nKVH;
-                        T* dst = static_cast<T*>(is_k ? r.kcache : r.vcache) + ((size_t(m) * r.nKVH + kvh) * r.max_seq + pos) * r.D;
-                        dst[d] = o0; dst[d + half] = o1;
-                    }
+                    ++uses; if (++stage == nstages) { stage = 0; phase ^= 1u; }
                 }
             }
-        } else if (threadIdx.x < 64 * R) {
-            const int l = threadIdx.x % 32, c = threadIdx.x / 32;
-            float v = 0.f;
-            #pragma unroll
-            for (int w = 0; w < kSkinnyWarps; ++w) v += red[parity][w][l][c];
-            const int m = 2 * (l % 4) + (c & 1), n = grp * 8 * R + l / 4 + 8 * (c >> 1);
-            if (m < a.M && n < a.N) {
-                const size_t idx = size_t(m) * a.ldo + n;
-                if (EPI == EPI_STORE16)      static_cast<T*>(a.out)[idx] = from_float<T>(v);
-                else if (EPI == EPI_STORE32) static_cast<float*>(a.out)[idx] = v;
-                else if (grp == int(blockIdx.x)) static_cast<float*>(a.out)[idx] = prev + v;
-                else                         static_cast<float*>(a.out)[idx] += v;
-            }
+            if (!ok) atomicExch(status, 1);
         }
+    } else {
+        // ---- consumers ------------------------------------------------------------------------------------------
+        const int g = lane / 4, t4 = lane % 4;
+        griddep_wait();                                           // activations come from earlier kernels of the stream
+        skinny_prologue<T, PRO>(a, xs, part_ss, Mp, warp, lane);
+        const T* xrow = xs + size_t(g) * xstride + t4 * 16;
+        int stage = 0; uint32_t phase = 0;
+        int parity = 0;
+        bool ok = true;
+        for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x, parity ^= 1) {
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (int sl = 0; sl < nslab; ++sl) {
+                if (ok && !dme::wait(&full_bar[stage], phase, status)) ok = false;
+                const int c0 = sl * slab, cols = min(slab, K - c0);
+                const int nblk = (cols + 63) / 64;
+                const unsigned char* st = stages + size_t(stage) * stage_bytes;
+                if (ok) {
+                    for (int blk = warp; blk < nblk; blk += kSkinnyWarps) {       // warp-uniform
+                        const bool live = blk * 64 + t4 * 16 < cols;
+                        uint4 wa0 = make_uint4(0u, 0u, 0u, 0u), wa1 = wa0, wb0 = wa0, wb1 = wa0, xa = wa0, xb = wa0;
+                        if (live) {
+                            const uint4* pa = reinterpret_cast<const uint4*>(st + size_t(g) * rowb + (blk * 64 + t4 * 16) * 2);
+                            const uint4* pb = reinterpret_cast<const uint4*>(st + size_t(g + 8) * rowb + (blk * 64 + t4 * 16) * 2);
+                            wa0 = pa[0]; wa1 = pa[1]; wb0 = pb[0]; wb1 = pb[1];
+                            if (g < Mp) {
+                                const uint4* xp = reinterpret_cast<const uint4*>(xrow + c0 + blk * 64);
+                                xa = xp[0]; xb = xp[1];
+                            }
+                        }
+                        const uint32_t wA[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
+                        const uint32_t wB[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
+                        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                        #pragma unroll
+                        for (int s = 0; s < 4; ++s) {
+                            const uint32_t af[4] = {wA[2 * s], wB[2 * s], wA[2 * s + 1], wB[2 * s + 1]};
+                            mma_16816<T>(acc, af, xw[2 * s], xw[2 * s + 1]);
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) dme::mbar_arrive(&empty_bar[stage]);
+                if (++stage == nstages) { stage = 0; phase ^= 1u; }
+            }
+            *reinterpret_cast<float4*>(&red[parity][warp][lane][0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            skinny_barrier();
+            skinny_epilogue<T, EPI, 2>(a, red[parity], grp, threadIdx.x, false, 0.f);
+        }
+        if (!ok && lane == 0) atomicExch(status, 1);
     }
 }
 
@@ -334,6 +477,33 @@ int launch_skinny(const SkinnyArgs& a, cudaStream_t st) {
     if (EPI == EPI_ROPE && (a.rope.D % 16 != 0 || a.N != (a.rope.nQH + 2 * a.rope.nKVH) * a.rope.D)) return B200P_E_RANGE;
     const int sms = sm_count() > 0 ? sm_count() : 148;
     constexpr bool paired = EPI == EPI_SILU16 || EPI == EPI_ROPE;
+    const bool pdl = tuning(KNOB_RUNTIME_PDL, 1) != 0;
+    if (tuning(KNOB_RUNTIME_SKINNY, 2) == 2) {
+        // W staged through shared memory by a producer thread (skinny_stream_kernel), one CTA per SM
+        const int slab_cols = kSkinnySlab;                               // measured: 0.67 ms per token at 2048, 0.72 at 1024, 0.73 at 4096
+        const int slab = a.K < slab_cols ? a.K : slab_cols;
+        const int stage_bytes = 16 * (slab * 2 + 16);
+        const int x_bytes = int((smem + 127) / 128 * 128);
+        int nstages = (224000 - x_bytes) / stage_bytes;
+        if (nstages > 8) nstages = 8;
+        int* status = device_status_ptr();
+        if (nstages >= 2 && status) {
+            const int groups = EPI == EPI_SILU16 ? (a.N + 7) / 8 : (a.N + 15) / 16;
+            const size_t dyn = size_t(x_bytes) + size_t(nstages) * stage_bytes;
+            void (*sk)(SkinnyArgs, int, int, int*) = skinny_stream_kernel<T, PRO, EPI>;
+            const cudaError_t ae = cudaFuncSetAttribute(sk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn));
+            if (ae != cudaSuccess) return int(ae);
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3(groups < sms ? groups : sms); cfg.blockDim = dim3(kSkinnyStreamThreads); cfg.dynamicSmemBytes = dyn; cfg.stream = st;
+            cudaLaunchAttribute attr[1];
+            attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[0].val.programmaticStreamSerializationAllowed = 1;
+            cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
+            const cudaError_t le = cudaLaunchKernelEx(&cfg, sk, a, nstages, slab_cols, status);
+            g_launches.fetch_add(1, std::memory_order_relaxed);
+            return le == cudaSuccess ? B200P_OK : int(le);
+        }
+    }
     // 8-row groups when 16-row groups would leave a third of the CTA slots (2 per SM) empty
     const bool half_rows = !paired && (a.N + 15) / 16 < (4 * sms) / 3;
     const int ngroups = EPI == EPI_SILU16 ? (a.N + 7) / 8 : half_rows ? (a.N + 7) / 8 : (a.N + 15) / 16;
@@ -351,7 +521,7 @@ int launch_skinny(const SkinnyArgs& a, cudaStream_t st) {
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr; cfg.numAttrs = tuning(KNOB_RUNTIME_PDL, 1) != 0 ? 1 : 0;
+    cfg.attrs = attr; cfg.numAttrs = pdl ? 1 : 0;
     const cudaError_t le = cudaLaunchKernelEx(&cfg, kern, a);
     g_launches.fetch_add(1, std::memory_order_relaxed);
     return le == cudaSuccess ? B200P_OK : int(le);

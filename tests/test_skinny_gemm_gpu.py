@@ -9,6 +9,15 @@ import oracle as orc
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture(params=[1, 2], ids=["weights-in-registers", "weights-through-shared-memory"], autouse=True)
+def skinny_kernel(b200p, request):
+    """Every test runs on both kernels: W held in registers between load and MMA, and W staged
+    through a shared-memory ring by a producer thread."""
+    b200p.set_tuning("runtime_skinny", request.param)
+    yield request.param
+    b200p.set_tuning("runtime_skinny", -1)
+
+
 def w16(torch, rng, shape, kind, scale=1.0):
     a = orc.round_to((rng.standard_normal(shape) * scale).astype(np.float32), kind)
     t = torch.from_numpy(a).cuda()
