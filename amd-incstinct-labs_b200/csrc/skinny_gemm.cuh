@@ -34,6 +34,12 @@
 //
 // Same arithmetic contract as the GEMM path: 16-bit operands, fp32 products and
 // sums, outputs rounded once.
+//
+// Two kernels share the fragment scheme, the prologue and the epilogues:
+// skinny_gemm_kernel as described above (W goes from global memory to registers to
+// the MMA), and skinny_stream_kernel further down, the default, in which a producer
+// thread stages W through a shared-memory ring so that loads run ahead across row
+// groups and the bytes in flight are not bounded by registers.
 // ---------------------------------------------------------------------------
 #pragma once
 #include "common.cuh"
