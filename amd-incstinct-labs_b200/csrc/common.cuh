@@ -34,9 +34,24 @@ enum Knob {
     KNOB_COUNT
 };
 
-// Device address of the library's status word on the current device (raised by
-// kernels whose bounded wait gave up), or nullptr without a device.
+// Device address of the library's sticky status word on the current device: raised at
+// kernel exit by any kernel one of whose bounded waits gave up, reported and cleared by
+// b200p_device_status.  nullptr without a device.
 int* device_status_ptr();
+
+// Per-launch scratch words.  Every launch of a kernel with bounded waits or a device-side
+// work counter takes the next slot of a ring of kLaunchSlots slots on the current device
+// and clears it on its own stream before the kernel:
+//   work  : zero at launch; persistent CTAs draw their later work items from it;
+//   abort : zero at launch; set by the first wait of THIS launch that gives up and polled
+//           by its other waits, so one lost copy ends the launch within about one wait
+//           limit -- and never touches a launch that is in flight on another stream.
+// The ring wraps: at most kLaunchSlots such launches may be enqueued and unfinished on a
+// device at a time.
+constexpr unsigned kLaunchSlots = 1024;
+struct LaunchSlot { int* work; int* abort; };
+// B200P_OK, B200P_E_NO_DEVICE or the cudaError_t of the clearing memset.
+int take_launch_slot(cudaStream_t st, LaunchSlot* out);
 
 inline bool aligned(const void* p, size_t a) { return (reinterpret_cast<uintptr_t>(p) & (a - 1)) == 0; }
 

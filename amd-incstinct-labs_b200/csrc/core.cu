@@ -32,6 +32,46 @@ int sm_count() {
     return sms;
 }
 
+// Sticky status word and the per-launch slot ring (see common.cuh).  Kernels receive
+// addresses inside these arrays as parameters; only this file names the symbols.
+__device__ int g_device_status = 0;
+__device__ int g_launch_slots[kLaunchSlots][2];
+
+namespace {
+struct DevicePtrs { int* status; int* slots; };
+DevicePtrs* device_ptrs() {
+    static DevicePtrs ptrs[kMaxDevices] = {};
+    static std::mutex mu;
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) { cudaGetLastError(); return nullptr; }
+    std::lock_guard<std::mutex> lock(mu);
+    if (!ptrs[dev].status) {
+        void *a = nullptr, *b = nullptr;
+        if (cudaGetSymbolAddress(&a, g_device_status) != cudaSuccess || cudaGetSymbolAddress(&b, g_launch_slots) != cudaSuccess) {
+            cudaGetLastError();
+            return nullptr;
+        }
+        ptrs[dev].status = static_cast<int*>(a); ptrs[dev].slots = static_cast<int*>(b);
+    }
+    return &ptrs[dev];
+}
+std::atomic<unsigned> g_next_slot{0};
+} // namespace
+
+int* device_status_ptr() {
+    DevicePtrs* d = device_ptrs();
+    return d ? d->status : nullptr;
+}
+
+int take_launch_slot(cudaStream_t st, LaunchSlot* out) {
+    DevicePtrs* d = device_ptrs();
+    if (!d) return B200P_E_NO_DEVICE;
+    int* base = d->slots + 2 * (g_next_slot.fetch_add(1, std::memory_order_relaxed) % kLaunchSlots);
+    if (cudaError_t e = cudaMemsetAsync(base, 0, 2 * sizeof(int), st)) return int(e);
+    out->work = base; out->abort = base + 1;
+    return B200P_OK;
+}
+
 unsigned tuning_epoch() { return g_tuning_epoch.load(std::memory_order_relaxed); }
 
 int tuning(int knob, int dflt) {
@@ -58,12 +98,22 @@ extern "C" const char* b200p_strerror(int s) {
         case B200P_E_NO_DEVICE: return "no usable CUDA device";
         case B200P_E_TIMEOUT:   return "a bounded device-side wait gave up";
         case B200P_E_RANGE:     return "size beyond a documented maximum";
+        case B200P_E_IO:        return "model file missing, short or malformed";
     }
     if (s > 0) return cudaGetErrorString(static_cast<cudaError_t>(s));
     return "unknown status";
 }
 
 extern "C" unsigned long long b200p_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+extern "C" int b200p_device_status(int clear) {
+    int h = 0;
+    cudaError_t e = cudaDeviceSynchronize();
+    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&h, g_device_status, sizeof(int));
+    if (e == cudaSuccess && clear && h != 0) { const int z = 0; e = cudaMemcpyToSymbol(g_device_status, &z, sizeof(z)); }
+    if (e != cudaSuccess) return int(e);
+    return h == 0 ? B200P_OK : B200P_E_TIMEOUT;
+}
 
 extern "C" int b200p_set_tuning(const char* key, int value) {
     if (!key) return INT_MIN;

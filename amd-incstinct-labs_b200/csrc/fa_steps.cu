@@ -52,7 +52,7 @@ template <> __device__ __forceinline__ float exp_for<__nv_bfloat16>(float x) { r
 template <typename T, int D, int STEP>
 __global__ void __launch_bounds__(kBr * 32)
 fa_step_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __restrict__ V, T* __restrict__ O,
-               int seq_q, int seq_k, int heads, float scale, int* status) {
+               int seq_q, int seq_k, int heads, float scale, int* abort_word, int* sticky) {
     constexpr int DPL = D / 32;                           // output dims per lane
     constexpr uint32_t kTileBytes = kBc * D * sizeof(T);
     extern __shared__ __align__(128) unsigned char smem[];
@@ -105,7 +105,7 @@ fa_step_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __rest
                 dme::copy_tile_1d(Kt + nb * kBc * D, Kb + size_t(j + 1) * kBc * D, kTileBytes, &full[nb]);
                 dme::copy_tile_1d(Vt + nb * kBc * D, Vb + size_t(j + 1) * kBc * D, kTileBytes, &full[nb]);
             }
-            if (!dme::wait(&full[buf], uint32_t(j >> 1) & 1u, status)) { ok = false; }
+            if (!dme::wait(&full[buf], uint32_t(j >> 1) & 1u, abort_word)) { ok = false; }
         } else {
             // cooperative synchronous tile load, 16 bytes per thread per step
             const uint4* ks = reinterpret_cast<const uint4*>(Kb + size_t(j) * kBc * D);
@@ -153,18 +153,143 @@ fa_step_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __rest
     if (STEP == 2) {
         if (!ok) atomicExch(&s_failed, 1);
         __syncthreads();
-        if (threadIdx.x == 0 && s_failed) atomicExch(status - 1, 1);
+        if (threadIdx.x == 0 && s_failed) atomicExch(sticky, 1);
     }
+}
+
+// ---------------------------------------------------------------------------
+// The reference's fp32-I/O kernels, one query row per block (Br = 1):
+//   research/flash-attention-mi300x/kernels/fa_naive.hip:118-278   (DPP = false)
+//   research/flash-attention-mi300x/kernels/fa_dpp.hip:96-155,167-313 (DPP = true)
+// Bc keys per tile are spread over Bc/64 "waves"; here a wave is one 32-lane warp
+// holding the 64 scores as an adjacent pair per lane.  Row max and row sum are the
+// reference's two-phase reduction (block_reduce_max_sum): inside the wave with the
+// pair primitives (shfl_down order for the naive kernel), across the waves through
+// 2 * waves floats of shared memory.  Keys past seq_len are padded with the lowest
+// float and contribute p = 0 (kernels/fa_naive.hip:158-169,233); any seq_len works.
+// O[row] = sum_k p_k V[k] / l with l_inv = l > 0 ? 1/l : 0.
+// ---------------------------------------------------------------------------
+template <int BC, int D, bool DPP>
+__global__ void __launch_bounds__(BC / 2)
+fa_rows_f32_kernel(const float* __restrict__ Q, const float* __restrict__ K, const float* __restrict__ V,
+                   float* __restrict__ O, int seq_len, int n_heads, float scale) {
+    constexpr int WAVES = BC / 64, THREADS = BC / 2;
+    constexpr float kLowest = -3.402823466e+38f;
+    __shared__ __align__(16) float q_s[D];
+    __shared__ float p_s[BC];
+    __shared__ float red[2 * WAVES];
+    const int tid = threadIdx.x, wave_i = tid / 32, lane = tid % 32;
+    const int row = blockIdx.x, bh = blockIdx.y;               // bh = batch * n_heads + head
+    const size_t base = size_t(bh) * seq_len * D;
+    for (int d = tid; d < D; d += THREADS) q_s[d] = Q[base + size_t(row) * D + d];
+    __syncthreads();
+
+    float m = kLowest, l = 0.f;
+    constexpr int DPT = (D + THREADS - 1) / THREADS;           // output dims per thread: d = tid + i * THREADS
+    float o[DPT];
+    #pragma unroll
+    for (int i = 0; i < DPT; ++i) o[i] = 0.f;
+
+    const int tiles = (seq_len + BC - 1) / BC;
+    for (int j = 0; j < tiles; ++j) {
+        const int kv0 = j * BC;
+        const int k0 = kv0 + wave_i * 64 + 2 * lane, k1 = k0 + 1;
+        float s0 = kLowest, s1 = kLowest;
+        if (k0 < seq_len) {
+            const float4* kr = reinterpret_cast<const float4*>(K + base + size_t(k0) * D);
+            float a = 0.f;
+            #pragma unroll 4
+            for (int d4 = 0; d4 < D / 4; ++d4) {
+                const float4 kv = kr[d4]; const float4 qv = *reinterpret_cast<const float4*>(&q_s[4 * d4]);
+                a = fmaf(qv.x, kv.x, a); a = fmaf(qv.y, kv.y, a); a = fmaf(qv.z, kv.z, a); a = fmaf(qv.w, kv.w, a);
+            }
+            s0 = a * scale;
+        }
+        if (k1 < seq_len) {
+            const float4* kr = reinterpret_cast<const float4*>(K + base + size_t(k1) * D);
+            float a = 0.f;
+            #pragma unroll 4
+            for (int d4 = 0; d4 < D / 4; ++d4) {
+                const float4 kv = kr[d4]; const float4 qv = *reinterpret_cast<const float4*>(&q_s[4 * d4]);
+                a = fmaf(qv.x, kv.x, a); a = fmaf(qv.y, kv.y, a); a = fmaf(qv.z, kv.z, a); a = fmaf(qv.w, kv.w, a);
+            }
+            s1 = a * scale;
+        }
+        // phase 1: inside the wave; phase 2: across the waves of the block
+        float tmax = DPP ? wave::dpp::reduce_max_bcast(s0, s1) : portable_reduce_bcast(s0, s1, wave::MaxOp{});
+        if (WAVES > 1) {
+            if (lane == 0) red[wave_i] = tmax;
+            __syncthreads();
+            tmax = red[0];
+            #pragma unroll
+            for (int w = 1; w < WAVES; ++w) tmax = tmax > red[w] ? tmax : red[w];
+        }
+        const float m_new = fmaxf(m, tmax);                    // running max (fused_softmax.hpp:38-48)
+        const float p0 = k0 < seq_len ? expf(s0 - m_new) : 0.f;
+        const float p1 = k1 < seq_len ? expf(s1 - m_new) : 0.f;
+        float tsum = DPP ? wave::dpp::reduce_sum_bcast(p0, p1) : portable_reduce_bcast(p0, p1, wave::SumOp{});
+        if (WAVES > 1) {
+            if (lane == 0) red[WAVES + wave_i] = tsum;
+            __syncthreads();
+            tsum = red[WAVES];
+            #pragma unroll
+            for (int w = 1; w < WAVES; ++w) tsum += red[WAVES + w];
+        }
+        const float alpha = expf(m - m_new);
+        m = m_new;
+        l = alpha * l + tsum;
+        p_s[wave_i * 64 + 2 * lane] = p0;
+        p_s[wave_i * 64 + 2 * lane + 1] = p1;
+        __syncthreads();
+        const int live = min(BC, seq_len - kv0);
+        #pragma unroll
+        for (int i = 0; i < DPT; ++i) {
+            const int d = tid + i * THREADS;
+            if (d < D) {
+                float acc = o[i] * alpha;
+                const float* vcol = V + base + size_t(kv0) * D + d;
+                #pragma unroll 4
+                for (int k = 0; k < live; ++k) acc = fmaf(p_s[k], vcol[size_t(k) * D], acc);
+                o[i] = acc;
+            }
+        }
+        __syncthreads();                                       // p_s and red are rewritten by the next tile
+    }
+    const float l_inv = l > 0.f ? 1.f / l : 0.f;
+    #pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+        const int d = tid + i * THREADS;
+        if (d < D) O[base + size_t(row) * D + d] = o[i] * l_inv;
+    }
+}
+
+template <int BC, int D>
+int launch_rows(bool dpp, const float* Q, const float* K, const float* V, float* O, int batch, int heads, int seq_len,
+                float scale, cudaStream_t st) {
+    const dim3 grid(unsigned(seq_len), unsigned(batch) * unsigned(heads));
+    if (dpp) fa_rows_f32_kernel<BC, D, true><<<grid, BC / 2, 0, st>>>(Q, K, V, O, seq_len, heads, scale);
+    else     fa_rows_f32_kernel<BC, D, false><<<grid, BC / 2, 0, st>>>(Q, K, V, O, seq_len, heads, scale);
+    return launched();
+}
+template <int D>
+int launch_rows_bc(int bc, bool dpp, const float* Q, const float* K, const float* V, float* O, int batch, int heads,
+                   int seq_len, float scale, cudaStream_t st) {
+    switch (bc) {
+        case 64:  return launch_rows<64, D>(dpp, Q, K, V, O, batch, heads, seq_len, scale, st);
+        case 128: return launch_rows<128, D>(dpp, Q, K, V, O, batch, heads, seq_len, scale, st);
+        case 256: return launch_rows<256, D>(dpp, Q, K, V, O, batch, heads, seq_len, scale, st);
+    }
+    return B200P_E_OP;
 }
 
 template <typename T, int D, int STEP>
 int launch_step(const void* Q, const void* K, const void* V, void* O, int batch, int heads, int seq_q, int seq_k,
                 float scale, cudaStream_t st) {
     const size_t smem = 4 * size_t(kBc) * D * sizeof(T) + (kBr * kBc + kBr * D) * sizeof(float) + 64;
-    int* status = device_status_ptr();
-    if (!status) return B200P_E_NO_DEVICE;
-    status += 1;                                               // per-launch abort word; [0] is the sticky report
-    if (STEP == 2) { if (cudaError_t ce = cudaMemsetAsync(status, 0, sizeof(int), st)) return int(ce); }
+    int* sticky = device_status_ptr();
+    if (!sticky) return B200P_E_NO_DEVICE;
+    LaunchSlot slot{};                                         // the launch's own abort word (only the async step waits)
+    if (STEP == 2) { if (int se = take_launch_slot(st, &slot)) return se; }
     auto kern = fa_step_kernel<T, D, STEP>;
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
@@ -172,7 +297,7 @@ int launch_step(const void* Q, const void* K, const void* V, void* O, int batch,
     }
     const unsigned grid = unsigned(batch) * heads * (seq_q / kBr);
     kern<<<grid, kBr * 32, smem, st>>>(static_cast<const T*>(Q), static_cast<const T*>(K), static_cast<const T*>(V),
-                                       static_cast<T*>(O), seq_q, seq_k, heads, scale, status);
+                                       static_cast<T*>(O), seq_q, seq_k, heads, scale, slot.abort, sticky);
     return launched();
 }
 template <typename T, int D>
@@ -197,6 +322,22 @@ int launch_step_d(int step, int D, const void* Q, const void* K, const void* V, 
 
 using namespace b200p;
 
+extern "C" int b200p_fa_rows_f32(int variant, int bc, const float* Q, const float* K, const float* V, float* O,
+                                 int batch, int heads, int seq_len, int D, float scale, b200p_stream_t stream) {
+    if (variant != 0 && variant != 1) return B200P_E_OP;
+    if (bc != 64 && bc != 128 && bc != 256) return B200P_E_OP;
+    if (D != 64 && D != 128) return B200P_E_DIM;
+    if (batch <= 0 || heads <= 0 || seq_len <= 0) return B200P_E_LENGTH;
+    if ((long long)batch * heads > 65535) return B200P_E_RANGE;
+    if (!Q || !K || !V || !O) return B200P_E_NULL;
+    if (!aligned(Q, 16) || !aligned(K, 16) || !aligned(V, 16) || !aligned(O, 16)) return B200P_E_ALIGN;
+    if (sm_count() <= 0) return B200P_E_NO_DEVICE;
+    if (scale == 0.f) scale = 1.f / sqrtf(float(D));
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return D == 64 ? launch_rows_bc<64>(bc, variant == 1, Q, K, V, O, batch, heads, seq_len, scale, st)
+                   : launch_rows_bc<128>(bc, variant == 1, Q, K, V, O, batch, heads, seq_len, scale, st);
+}
+
 extern "C" int b200p_fa_step(int step, int dtype, const void* Q, const void* K, const void* V, void* O,
                              int batch, int heads, int seq_q, int seq_k, int D, float scale, b200p_stream_t stream) {
     if (step < 0 || step > 3) return B200P_E_OP;
@@ -213,9 +354,15 @@ extern "C" int b200p_fa_step(int step, int dtype, const void* Q, const void* K, 
         b200p_prefill_cfg c{D, seq_q, seq_k, heads, heads, batch, 0};
         return prefill_dispatch(Q, K, V, O, &c, dtype, nullptr, st);
     }
-    if (seq_q % kBr != 0 || seq_k % kBc != 0) return B200P_E_LENGTH;      // the reference's tiling
     if (sm_count() <= 0) return B200P_E_NO_DEVICE;
     if (scale == 0.f) scale = 1.f / sqrtf(float(D));
+    if (seq_q % kBr != 0 || seq_k % kBc != 0) {
+        // Lengths off the Br = 16 / Bc = 64 tiling: the fp32-I/O kernels take any seq_len by padding the
+        // keys past the end (kernels/fa_naive.hip:158-169); the 16-bit step kernels keep the reference's tiling.
+        if (dtype != B200P_F32 || seq_q != seq_k) return B200P_E_LENGTH;
+        return b200p_fa_rows_f32(step == 0 ? 0 : 1, 64, static_cast<const float*>(Q), static_cast<const float*>(K),
+                                 static_cast<const float*>(V), static_cast<float*>(O), batch, heads, seq_q, D, scale, stream);
+    }
     switch (dtype) {
         case B200P_F16:  return launch_step_d<__half>(step, D, Q, K, V, O, batch, heads, seq_q, seq_k, scale, st);
         case B200P_BF16: return launch_step_d<__nv_bfloat16>(step, D, Q, K, V, O, batch, heads, seq_q, seq_k, scale, st);

@@ -46,40 +46,6 @@
 
 namespace b200p {
 
-// [0]: sticky, reported by b200p_device_status; [1]: abort flag of the launch in flight (cleared by
-// every launcher on its stream), polled by the bounded waits so that one failed wait ends the launch.
-__device__ int g_device_status[2] = {0, 0};
-
-// Work counters of the persistent prefill kernel: each launch takes the next slot (cleared on its stream
-// before the kernel), so launches in flight on different streams do not share one.
-constexpr unsigned kWorkSlots = 1024;
-__device__ int g_prefill_work[kWorkSlots];
-
-static int* prefill_work_slot() {
-    static int* base[64] = {};
-    static std::atomic<unsigned> next{0};
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return nullptr; }
-    if (!base[dev]) {
-        void* ptr = nullptr;
-        if (cudaGetSymbolAddress(&ptr, g_prefill_work) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-        base[dev] = static_cast<int*>(ptr);
-    }
-    return base[dev] + next.fetch_add(1, std::memory_order_relaxed) % kWorkSlots;
-}
-
-int* device_status_ptr() {
-    static int* ptrs[64] = {};
-    int dev = -1;
-    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return nullptr; }
-    if (!ptrs[dev]) {
-        void* p = nullptr;
-        if (cudaGetSymbolAddress(&p, g_device_status) != cudaSuccess) { cudaGetLastError(); return nullptr; }
-        ptrs[dev] = static_cast<int*>(p);
-    }
-    return ptrs[dev];
-}
-
 namespace {
 
 constexpr int kBM = 128;                 // query rows per tile
@@ -88,13 +54,8 @@ constexpr int kBN = 128;                 // keys per tile
 // warps (tile, lane quarter), the next warpgroup holds the MMA and the TMA warp.
 constexpr int prefill_threads(int RS) { return (8 * RS + 4) * 32; }
 constexpr float kLazyRescale = 8.0f;     // log2 units
-#ifndef B200P_POLY_EVERY
-#define B200P_POLY_EVERY 0
-#endif
-constexpr int kPolyEvery = B200P_POLY_EVERY;
-// The debug instantiation (DBG, used by b200p_attn_prefill_debug only) can write the raw scores of the first
-// tile or clock64 stamps of the first work item's steps to the debug buffer; the production instantiation carries
-// neither: the stamps alone cost the softmax warps enough registers to spill.   // 0: all exponentials on the SFU; n: one pair in n on the FMA pipes
+// The debug instantiation (DBG, used by b200p_attn_prefill_debug only) writes the raw scores of the first
+// tile to the debug buffer; the production instantiation does not carry that code.
 
 template <int D> struct PrefillShape {
     static constexpr int SUB = D / 64;                         // 64-element boxes per row
@@ -113,10 +74,11 @@ struct PrefillParams {
     void* O;
     long long o_seq, o_head, o_batch;   // element strides of O
     float* debug_s;            // optional: raw S of tile (0,0) of CTA (0,0,0), [128][128] fp32
-    int* status;               // the library's device status word: raised by a wait that gave up, polled by all waits
-    long long* timeline;       // optional (tuning aid): clock64 stamps of CTA (0,0,0), 16 slots per KV tile
+    int* status;               // this launch's abort word: raised by a wait that gave up, polled by all its waits
+    int* sticky;               // the library's sticky status word, raised at exit by a CTA that saw a failed wait
     int* work_counter;         // zero at launch: the CTAs draw the ids of their later work items from it
     int seqQ, seqK, nQH, nKVH, group, batch, causal;
+    int o_vec32;               // O and all of its strides are multiples of 32 bytes: the epilogue stores whole sectors
     float scale_log2;
 };
 
@@ -300,7 +262,6 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                 tc::commit(&k_empty[kr.stage]);
                 kr.advance();
                 if (nmax == 1) tc::commit(q_empty);
-                const bool dbg = DBG && p.timeline && id == 0;
                 // one tile's share of step j: P.V over the two halves of P as they arrive, then the next Q.K^T
                 auto tile_step = [&](auto tc_t, int j, int nt, int cst, int cot) -> bool {
                     constexpr int t = decltype(tc_t)::value;
@@ -309,15 +270,12 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                     // the first P.V of an item overwrites O_t: the previous item's epilogue must have read it
                     if (j == 0 && cot > 0 && !dme::wait(&o_free[t], uint32_t((cot - 1) & 1), p.status)) return false;
                     tc::fence_after_sync();
-                    const bool stamp = dbg && j < 64;
-                    if (stamp) p.timeline[j * 16 + 8 + 2 * t] = clock64();
                     issue_pv(t, vr.stage, j == 0, 0);                 // keys 0..63 while the softmax finishes 64..127
                     if (!dme::wait(&p_half[2 * t + 1], uint32_t((cst + j) & 1), p.status)) return false;
                     tc::fence_after_sync();
                     issue_pv(t, vr.stage, j == 0, kBN / 32);
                     if (j + 1 < nt) { issue_qk(t, kr.stage); tc::commit(&s_full[t]); }
                     else tc::commit(&o_done[t]);
-                    if (stamp) p.timeline[j * 16 + 9 + 2 * t] = clock64();
                     return true;
                 };
                 for (int j = 0; j < nmax && ok; ++j) {
@@ -365,8 +323,6 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
           for (int j = 0; j < nt; ++j) {
             if (!dme::wait(&s_full[t], uint32_t((cs + j) & 1), p.status)) { ok = false; break; }
             tc::fence_after_sync();
-            const bool stamp = DBG && p.timeline && r == 0 && half == 0 && id == 0 && j < 64;
-            if (stamp) p.timeline[j * 16 + 4 * t + 0] = clock64();
             const bool need_mask = (p.causal && j * kBN + kBN - 1 > q0t) || (j * kBN + kBN > p.seqK);
             // columns (of this thread's range) <= col_limit are live
             const int col_limit = min(p.causal ? row : 0x7fffffff, p.seqK - 1) - j * kBN - half * CW;
@@ -375,7 +331,6 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             #pragma unroll
             for (int c = 0; c < CW / 32; ++c) tc::ld_32x32b_x32(tS + half * CW + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&sv[c * 32]));
             tc::wait_ld();
-            if (stamp) p.timeline[j * 16 + 4 * t + 1] = clock64();
             if (DBG && p.debug_s && j == 0 && t == 0 && id == 0) {
                 #pragma unroll
                 for (int i = 0; i < CW; ++i) p.debug_s[r * kBN + half * CW + i] = __uint_as_float(sv[i]);
@@ -394,7 +349,6 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             const float m_new = mx * p.scale_log2;
             float alpha = 1.f;
             if (m_new > m_used + kLazyRescale) { alpha = fast_exp2(m_used - m_new); m_used = m_new; }
-            if (stamp) p.timeline[j * 16 + 4 * t + 2] = clock64();
             // ---- rescale O when some row of this warp moved its max (never on the first tile) ----
             if (j > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {
                 #pragma unroll
@@ -416,10 +370,8 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                 uint32_t pk[16];
                 #pragma unroll
                 for (int i = 0; i < 16; ++i) {
-                    // every kPolyEvery-th pair takes the FMA-pipe polynomial instead of the SFU
                     const float s0 = __uint_as_float(sv[c * 32 + 2 * i]), s1 = __uint_as_float(sv[c * 32 + 2 * i + 1]);
-                    const float2 e = (kPolyEvery > 0 && i % kPolyEvery == kPolyEvery - 1) ? exp2_pair_poly(s0, s1, p.scale_log2, neg_m)
-                                                                                          : exp2_pair(s0, s1, p.scale_log2, neg_m);
+                    const float2 e = exp2_pair(s0, s1, p.scale_log2, neg_m);
                     sv[c * 32 + 2 * i] = __float_as_uint(e.x); sv[c * 32 + 2 * i + 1] = __float_as_uint(e.y);
                     pk[i] = pack2<T>(e.x, e.y);
                 }
@@ -438,7 +390,6 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                 for (int u = 0; u < 4; ++u) la[u] += __uint_as_float(sv[i + u]);
             }
             l = l * alpha + ((la[0] + la[1]) + (la[2] + la[3]));
-            if (stamp) p.timeline[j * 16 + 4 * t + 3] = clock64();
           }
           if (!ok) break;
           // ---- epilogue: O / l -> 16-bit; a thread writes its OW output columns of its row.  O is taken into
@@ -455,6 +406,17 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             if (row < p.seqQ) {
                 const float inv = l > 0.f ? 1.f / l : 1.f;
                 T* orow = static_cast<T*>(p.O) + size_t(o_b) * p.o_batch + size_t(o_head) * p.o_head + size_t(row) * p.o_seq + half * OW;
+                // 32-byte stores (whole sectors) where the rows of O allow them, else 16-byte stores
+                if (p.o_vec32) {
+                #pragma unroll
+                for (int q16 = 0; q16 < OW / 16; ++q16) {
+                    uint32_t o8[8];
+                    #pragma unroll
+                    for (int u = 0; u < 8; ++u) o8[u] = pack2<T>(__uint_as_float(v[q16 * 16 + 2 * u]) * inv, __uint_as_float(v[q16 * 16 + 2 * u + 1]) * inv);
+                    asm volatile("st.global.v8.b32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};"
+                                 :: "r"(o8[0]), "r"(o8[1]), "r"(o8[2]), "r"(o8[3]), "r"(o8[4]), "r"(o8[5]), "r"(o8[6]), "r"(o8[7]), "l"(orow + q16 * 16) : "memory");
+                }
+                } else {
                 #pragma unroll
                 for (int q8 = 0; q8 < OW / 8; ++q8) {
                     uint4 o4;
@@ -463,6 +425,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                     o4.z = pack2<T>(__uint_as_float(v[q8 * 8 + 4]) * inv, __uint_as_float(v[q8 * 8 + 5]) * inv);
                     o4.w = pack2<T>(__uint_as_float(v[q8 * 8 + 6]) * inv, __uint_as_float(v[q8 * 8 + 7]) * inv);
                     *reinterpret_cast<uint4*>(orow + q8 * 8) = o4;
+                }
                 }
             }
           }
@@ -474,7 +437,7 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
     __syncthreads();
     tc::fence_after_sync();
     if (warp == kMmaWarp) tc::tmem_dealloc(tmem, 512);
-    if (threadIdx.x == 0 && s_failed) atomicExch(p.status - 1, 1);
+    if (threadIdx.x == 0 && s_failed) atomicExch(p.sticky, 1);
 }
 
 template <typename T, int D, int RS>
@@ -504,21 +467,17 @@ int launch_prefill_rs(const void* Q, const void* K, const void* V, void* O, cons
         attr_set[dev][dbg] = true;
     }
     PrefillParams p{};
-    p.O = O; p.debug_s = debug_s; p.timeline = nullptr;
-    p.status = device_status_ptr();
-    if (!p.status) return B200P_E_NO_DEVICE;
-    p.status += 1;                                              // the per-launch abort word
-    if (cudaError_t ce = cudaMemsetAsync(p.status, 0, sizeof(int), st)) return int(ce);
-    if (debug_s && (tuning(KNOB_PREFILL_VARIANT, 0) & 256)) {      // tuning aid: the debug buffer receives the timeline
-        p.timeline = reinterpret_cast<long long*>(debug_s); p.debug_s = nullptr;
-    }
+    p.O = O; p.debug_s = debug_s;
+    p.sticky = device_status_ptr();
+    LaunchSlot slot{};
+    if (!p.sticky) return B200P_E_NO_DEVICE;
+    if (int se = take_launch_slot(st, &slot)) return se;       // work counter and abort word of this launch, cleared on its stream
+    p.status = slot.abort; p.work_counter = slot.work;
     p.o_seq = s.o_seq; p.o_head = s.o_head; p.o_batch = s.o_batch;
+    p.o_vec32 = aligned(O, 32) && s.o_seq % 16 == 0 && s.o_head % 16 == 0 && s.o_batch % 16 == 0;
     p.seqQ = c->seqQ; p.seqK = c->seqK; p.nQH = c->nQHeads; p.nKVH = c->nKVHeads; p.group = c->nQHeads / c->nKVHeads;
     p.batch = c->batch; p.causal = c->causal;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(D));
-    p.work_counter = prefill_work_slot();
-    if (!p.work_counter) return B200P_E_NO_DEVICE;
-    if (cudaError_t ce = cudaMemsetAsync(p.work_counter, 0, sizeof(int), st)) return int(ce);
     // One persistent CTA per SM (the kernel takes all of an SM's shared and tensor memory), or one CTA per
     // work item when the knob's bit 1 is set.
     const long long items = (long long)((c->seqQ + 2 * kBM - 1) / (2 * kBM)) * c->nQHeads * c->batch;
@@ -598,13 +557,4 @@ extern "C" int b200p_attn_prefill_debug(const void* Q, const void* K, const void
                                         const b200p_prefill_cfg* cfg, int dtype, float* raw_scores,
                                         b200p_stream_t stream) {
     return prefill_dispatch(Q, K, V, O, cfg, dtype, raw_scores, static_cast<cudaStream_t>(stream));
-}
-
-extern "C" int b200p_device_status(int clear) {
-    int h = 0;
-    cudaError_t e = cudaDeviceSynchronize();
-    if (e == cudaSuccess) e = cudaMemcpyFromSymbol(&h, g_device_status, sizeof(int));
-    if (e == cudaSuccess && clear && h != 0) { int z[2] = {0, 0}; e = cudaMemcpyToSymbol(g_device_status, z, sizeof(z)); }
-    if (e != cudaSuccess) return int(e);
-    return h == 0 ? B200P_OK : B200P_E_TIMEOUT;
 }

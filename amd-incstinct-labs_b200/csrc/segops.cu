@@ -271,10 +271,48 @@ segscan_lane_kernel(const S* __restrict__ in, S* __restrict__ out, size_t nseg) 
     }
 }
 
+// ---------------------------------------------------------------------------
+// Sum of 16-bit inputs, one whole segment per lane, in the association the
+// reference's 16-bit overloads prescribe: fp32, elements (i, i + 32) first, then
+// (i, i + 16), ... (the shfl_down loop of wave_reduce.hpp:48-63).  With the
+// segment in one lane's registers that tree costs 63 adds and no shuffle, so the
+// result agrees with the reference bit for bit at streaming speed.  A warp reads
+// 32 adjacent 128-byte lines and writes 32 adjacent results.
+// ---------------------------------------------------------------------------
+template <typename S, typename O, typename Op, int BYTES>
+__global__ void __launch_bounds__(kThreads)
+segreduce_lane_kernel(const S* __restrict__ in, O* __restrict__ out, size_t nseg) {
+    using C = Codec<S>;
+    static_assert(sizeof(S) == 2, "16-bit storage");
+    constexpr int W = BYTES / 4, NV = 128 / BYTES, EPV = BYTES / 2;
+    const char* src = reinterpret_cast<const char*>(in);
+    const Op op{};
+    const size_t stride = size_t(gridDim.x) * kThreads;
+    for (size_t seg = size_t(blockIdx.x) * kThreads + threadIdx.x; seg < nseg; seg += stride) {
+        uint32_t w[NV][W];
+        #pragma unroll
+        for (int j = 0; j < NV; ++j) VecIO<BYTES>::load(src + seg * 128 + size_t(j) * BYTES, w[j]);
+        float v[64];
+        #pragma unroll
+        for (int j = 0; j < NV; ++j) {
+            float t[EPV];
+            C::unpack(w[j], t);
+            #pragma unroll
+            for (int i = 0; i < EPV; ++i) v[j * EPV + i] = t[i];
+        }
+        const float r = wave::lane_reduce_shfl_down_order<64>(v, op);
+        if constexpr (std::is_same<O, float>::value) out[seg] = r;
+        else                                          out[seg] = C::narrow(r);
+    }
+}
+
 // --- single-wave probe through the public pair-per-lane API ----------------------
 template <typename T>
-__global__ void wave_probe_kernel(int fn, int op, const T* in, T* out) {
-    const unsigned l = threadIdx.x;
+__global__ void wave_probe_kernel(int fn, int op, const T* in, T* out, int nwaves) {
+    const int wave_i = int(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    if (wave_i >= nwaves) return;                              // whole warps leave together
+    in += size_t(wave_i) * 64; out += size_t(wave_i) * 64;
+    const unsigned l = threadIdx.x % 32;
     T a = in[2 * l], b = in[2 * l + 1];
     if (fn == 0) {
         T r;
@@ -291,8 +329,11 @@ __global__ void wave_probe_kernel(int fn, int op, const T* in, T* out) {
     }
 }
 template <typename N>
-__global__ void wave_probe_narrow_kernel(int fn, int op, const N* in, N* out) {
-    const unsigned l = threadIdx.x;
+__global__ void wave_probe_narrow_kernel(int fn, int op, const N* in, N* out, int nwaves) {
+    const int wave_i = int(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    if (wave_i >= nwaves) return;
+    in += size_t(wave_i) * 64; out += size_t(wave_i) * 64;
+    const unsigned l = threadIdx.x % 32;
     N a = in[2 * l], b = in[2 * l + 1];
     if (fn == 0) {
         N r;
@@ -303,6 +344,19 @@ __global__ void wave_probe_narrow_kernel(int fn, int op, const N* in, N* out) {
     } else {
         wave::scan_inclusive_sum(a, b);
         out[2 * l] = a; out[2 * l + 1] = b;
+    }
+}
+// Vote / bitwise wrappers on one wave: in[64] ints -> out[0..7] (see b200p_wave_vote_probe).
+__global__ void wave_vote_probe_kernel(const int* in, unsigned long long* out) {
+    const unsigned l = threadIdx.x % 32;
+    const int a = in[2 * l], b = in[2 * l + 1];
+    const unsigned long long bal = wave::ballot(a > 0, b > 0);
+    const int any_ = wave::any(a > 0, b > 0), all_ = wave::all(a > 0, b > 0), pc = wave::popcount(a > 0, b > 0);
+    const unsigned ra = wave::reduce_and(unsigned(a), unsigned(b)), ro = wave::reduce_or(unsigned(a), unsigned(b));
+    const unsigned long long b32 = wave::ballot(a > 0);
+    if (l == 5) {
+        out[0] = bal; out[1] = (unsigned long long)any_; out[2] = (unsigned long long)all_; out[3] = (unsigned long long)pc;
+        out[4] = ra; out[5] = ro; out[6] = b32; out[7] = wave::lane_mask_lt();
     }
 }
 
@@ -339,6 +393,16 @@ int reduce_op(int op, const void* in, void* out, size_t n, cudaStream_t st) {
 template <typename S, typename O>
 int reduce_bytes(int op, const void* in, void* out, size_t n, cudaStream_t st) {
     const bool wide = tuning(KNOB_SEG_VEC_BYTES, 32) == 32 && aligned(in, 32);
+    if constexpr (sizeof(S) == 2) {
+        // 16-bit sum: the reference's fp32 shfl_down association, a whole segment per lane
+        if (op == B200P_SUM) {
+            const size_t nseg = n / 64;
+            const int grid = grid_for((nseg + 31) / 32);
+            if (wide) segreduce_lane_kernel<S, O, wave::SumOp, 32><<<grid, kThreads, 0, st>>>(static_cast<const S*>(in), static_cast<O*>(out), nseg);
+            else      segreduce_lane_kernel<S, O, wave::SumOp, 16><<<grid, kThreads, 0, st>>>(static_cast<const S*>(in), static_cast<O*>(out), nseg);
+            return launched();
+        }
+    }
     return wide ? reduce_op<S, O, 32>(op, in, out, n, st) : reduce_op<S, O, 16>(op, in, out, n, st);
 }
 
@@ -465,22 +529,36 @@ extern "C" int b200p_segscan_exclusive_sum(int dtype, const void* in, void* out,
     return B200P_E_DTYPE;
 }
 
-extern "C" int b200p_wave_probe(int fn, int op, int dtype, const void* in, void* out, b200p_stream_t stream) {
+extern "C" int b200p_wave_probe_n(int fn, int op, int dtype, const void* in, void* out, int n_waves, b200p_stream_t stream) {
     if (fn < 0 || fn > 2) return B200P_E_OP;
     if (op < B200P_SUM || op > B200P_MIN) return B200P_E_OP;
     if (dtype < B200P_F32 || dtype > B200P_BF16) return B200P_E_DTYPE;
+    if (n_waves < 0) return B200P_E_LENGTH;
+    if (n_waves == 0) return B200P_OK;
     if (!in || !out) return B200P_E_NULL;
     if (sm_count() <= 0) return B200P_E_NO_DEVICE;
     const bool narrow = dtype == B200P_F16 || dtype == B200P_BF16;
     if (narrow && (fn == 2 || (fn == 1 && op != B200P_SUM))) return B200P_E_OP;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int wpb = 4, grid = (n_waves + wpb - 1) / wpb, tpb = (n_waves < wpb ? n_waves : wpb) * 32;
     switch (dtype) {
-        case B200P_F32:  wave_probe_kernel<float><<<1, 32, 0, st>>>(fn, op, (const float*)in, (float*)out); break;
-        case B200P_F64:  wave_probe_kernel<double><<<1, 32, 0, st>>>(fn, op, (const double*)in, (double*)out); break;
-        case B200P_I32:  wave_probe_kernel<int><<<1, 32, 0, st>>>(fn, op, (const int*)in, (int*)out); break;
-        case B200P_I64:  wave_probe_kernel<long long><<<1, 32, 0, st>>>(fn, op, (const long long*)in, (long long*)out); break;
-        case B200P_F16:  wave_probe_narrow_kernel<__half><<<1, 32, 0, st>>>(fn, op, (const __half*)in, (__half*)out); break;
-        case B200P_BF16: wave_probe_narrow_kernel<__nv_bfloat16><<<1, 32, 0, st>>>(fn, op, (const __nv_bfloat16*)in, (__nv_bfloat16*)out); break;
+        case B200P_F32:  wave_probe_kernel<float><<<grid, tpb, 0, st>>>(fn, op, (const float*)in, (float*)out, n_waves); break;
+        case B200P_F64:  wave_probe_kernel<double><<<grid, tpb, 0, st>>>(fn, op, (const double*)in, (double*)out, n_waves); break;
+        case B200P_I32:  wave_probe_kernel<int><<<grid, tpb, 0, st>>>(fn, op, (const int*)in, (int*)out, n_waves); break;
+        case B200P_I64:  wave_probe_kernel<long long><<<grid, tpb, 0, st>>>(fn, op, (const long long*)in, (long long*)out, n_waves); break;
+        case B200P_F16:  wave_probe_narrow_kernel<__half><<<grid, tpb, 0, st>>>(fn, op, (const __half*)in, (__half*)out, n_waves); break;
+        case B200P_BF16: wave_probe_narrow_kernel<__nv_bfloat16><<<grid, tpb, 0, st>>>(fn, op, (const __nv_bfloat16*)in, (__nv_bfloat16*)out, n_waves); break;
     }
+    return launched();
+}
+
+extern "C" int b200p_wave_probe(int fn, int op, int dtype, const void* in, void* out, b200p_stream_t stream) {
+    return b200p_wave_probe_n(fn, op, dtype, in, out, 1, stream);
+}
+
+extern "C" int b200p_wave_vote_probe(const int* in64, unsigned long long* out8, b200p_stream_t stream) {
+    if (!in64 || !out8) return B200P_E_NULL;
+    if (sm_count() <= 0) return B200P_E_NO_DEVICE;
+    wave_vote_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(in64, out8);
     return launched();
 }

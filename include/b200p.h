@@ -40,7 +40,8 @@ enum {
     B200P_E_WORKSPACE     = -7,   /* workspace missing or too small             */
     B200P_E_NO_DEVICE     = -8,   /* no usable CUDA device                      */
     B200P_E_TIMEOUT       = -9,   /* a bounded device-side wait gave up         */
-    B200P_E_RANGE         = -10   /* size beyond a documented maximum           */
+    B200P_E_RANGE         = -10,  /* size beyond a documented maximum           */
+    B200P_E_IO            = -11   /* a model file is missing, short or malformed */
 };
 
 /* ---- element types and ops ---------------------------------------------- */
@@ -93,6 +94,31 @@ int b200p_segscan_exclusive_sum(int dtype, const void* in, void* out,
  *     returns the input type). */
 int b200p_wave_probe(int fn, int op, int dtype, const void* in64, void* out64,
                      b200p_stream_t stream);
+
+/* b200p_wave_probe over n_waves independent waves (in/out: 64 * n_waves values),
+ * one warp per wave: the device-level API on arbitrary data. */
+int b200p_wave_probe_n(int fn, int op, int dtype, const void* in, void* out, int n_waves,
+                       b200p_stream_t stream);
+
+/* One wave through the vote and bitwise wrappers of wave64.cuh (the reference's
+ * research/wave-primitives/include/wave_primitives/wave_ballot.hpp:23-75 and
+ * wave_reduce.hpp reduce_and / reduce_or), pair per lane with predicate "value > 0":
+ * out8[0] ballot (64 bits, bit i = element i), [1] any, [2] all, [3] popcount,
+ * [4] reduce_and, [5] reduce_or of the 64 ints, [6] the 32-lane ballot of the lanes'
+ * first elements, [7] lane_mask_lt() of lane 5. */
+int b200p_wave_vote_probe(const int* in64, unsigned long long* out8, b200p_stream_t stream);
+
+/* Kernels that use the facade headers the way a caller of the reference would
+ * (cdna3-prims/tests/compile_smoke.hip:24-50; include <cdna3/cdna3.hpp> and
+ * <cdna3/examples/fused_softmax.hpp>):
+ *   which 0: cdna3::ex::row_softmax_lane over `rows` rows of 64 fp32 scores (pair per lane);
+ *   which 1: the same, rows of 32 scores, one per lane;
+ *   which 2: cdna3::ex::online_softmax_step over `tiles` 64-score tiles per row; out[row] =
+ *            (running max, denominator, sum of exp(s - max) accumulated like an O column);
+ *   which 3: dme::AsyncTile2D<16,64> ping/pong over `tiles` packed fp16 tiles (`in` is fp16),
+ *            out = 2 * in as fp32;
+ *   which 4: dme::copy_tile_1d_stream<float,256> per warp over `tiles` tiles, out = in + 1. */
+int b200p_api_probe(int which, const void* in, float* out, int rows, int tiles, b200p_stream_t stream);
 
 /* =========================================================================
  * FA2 attention.
@@ -220,13 +246,17 @@ int b200p_attn_merge_lse_wait(const b200p_peer_exchange* px, int seq, int rows, 
  * B200P_E_RANGE.  The first call on each device looks up the array's device
  * address; make that first call outside any stream capture.  All calls share
  * the one array: two calls whose kernels can overlap on the GPU (different
- * streams, no dependency) race on it -- serialise them. */
+ * streams, no dependency) race on it -- serialise them.  Two host threads that
+ * make their first call on a device at the same moment both perform the address
+ * look-up and store the same value, which is harmless.  A bounded wait that gave
+ * up inside such a call is reported by b200p_attn_workspace_status(NULL, stream). */
 int b200p_attn_decode_noalloc(const void* q, const void* K, const void* V, void* o,
                               const b200p_decode_args* args, b200p_stream_t stream);
 size_t b200p_attn_decode_noalloc_max_bytes(void);
 
 /* Synchronises `stream` and reports whether a kernel that used `workspace`
- * abandoned a bounded wait (B200P_E_TIMEOUT) or not (0). */
+ * abandoned a bounded wait (B200P_E_TIMEOUT) or not (0).  workspace = NULL names
+ * the built-in scratch of b200p_attn_decode_noalloc on the current device. */
 int b200p_attn_workspace_status(const void* workspace, b200p_stream_t stream);
 
 /* cdna3::attn::PrefillCfg, field for field (attention.hpp:63-71). */
@@ -288,9 +318,21 @@ int b200p_attn_prefill_debug(const void* Q, const void* K, const void* V, void* 
  * or, for steps 0-2, B200P_F32 -- the fp32-I/O kernels whose launch takes
  * (seq_len, n_heads, scale): research/flash-attention-mi300x/kernels/
  * fa_naive.hip:118-278, kernels/fa_dpp.hip:167-313.  scale = 0 means 1/sqrt(D).
- * seq_q % 16 == 0 and seq_k % 64 == 0 for steps 0-2 (the reference's tiling). */
+ * seq_q % 16 == 0 and seq_k % 64 == 0 for steps 0-2 (the reference's tiling), except
+ * B200P_F32 with seq_q == seq_k, which accepts any length (see b200p_fa_rows_f32). */
 int b200p_fa_step(int step, int dtype, const void* Q, const void* K, const void* V, void* O,
                   int batch, int heads, int seq_q, int seq_k, int D, float scale, b200p_stream_t stream);
+
+/* The reference's fp32-I/O kernels with one query row per block and Bc keys per
+ * tile over Bc/64 waves: research/flash-attention-mi300x/kernels/fa_naive.hip:118-278
+ * (variant 0, portable shuffle reductions) and kernels/fa_dpp.hip:96-155,167-313
+ * (variant 1, wave primitives + the two-phase block reduction).  Same launch
+ * arguments as the reference: (seq_len, n_heads, scale); Q,K,V,O [batch, heads,
+ * seq_len, D] fp32; bc 64, 128 or 256; any seq_len (keys past the end are padded
+ * as in kernels/fa_naive.hip:158-169); scale = 0 means 1/sqrt(D).
+ * b200p_fa_step with B200P_F32 and lengths off its tiling routes here with bc = 64. */
+int b200p_fa_rows_f32(int variant, int bc, const float* Q, const float* K, const float* V, float* O,
+                      int batch, int heads, int seq_len, int D, float scale, b200p_stream_t stream);
 
 /* Synchronises the device and reports whether any kernel of this library
  * abandoned a bounded wait since the last clear (B200P_E_TIMEOUT) or not (0). */

@@ -58,6 +58,22 @@ typedef struct b200p_model_weights {
     const b200p_layer_weights* layers;  /* host array of n_layers entries (device pointers inside) */
 } b200p_model_weights;
 
+/* cdna3::runtime::ModelLoader (model_loader.hpp:134-204): a model directory in the
+ * reference's export format -- meta.json plus one raw 16-bit .bin file per tensor
+ * (embed_tokens, lm_head, final_norm, layer_<i>_{q,k,v,o}_proj, layer_<i>_{q,k,v}_bias
+ * when meta has qkv_bias, layer_<i>_{gate,up,down}_proj, layer_<i>_norm_{attn,mlp}).
+ * The files hold fp16 bits unless meta.json says "dtype": "bf16".
+ * b200p_model_read_meta only parses meta.json (no device needed); b200p_model_load
+ * uploads every tensor into device memory that the model object owns;
+ * b200p_model_weights_of gives the table a session is created from (valid until
+ * b200p_model_free).  Failures are status codes (B200P_E_IO for a missing, short or
+ * malformed file), where the reference throws. */
+typedef struct b200p_model b200p_model;
+int b200p_model_read_meta(const char* model_dir, b200p_model_config* cfg, int* qkv_bias, int* dtype);
+b200p_model* b200p_model_load(const char* model_dir, int* status);
+const b200p_model_weights* b200p_model_weights_of(const b200p_model* model);
+void b200p_model_free(b200p_model* model);
+
 typedef struct b200p_session b200p_session;
 
 /* Session(model, max_seq) (session.hpp:253-259) for `batch` sequences.

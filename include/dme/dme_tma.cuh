@@ -85,12 +85,6 @@ __device__ __forceinline__ uint64_t policy_evict_first() {
     asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
     return p;
 }
-__device__ __forceinline__ uint64_t policy_evict_last() {
-    uint64_t p;
-    asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
-    return p;
-}
-
 // ---- copies (issued by ONE thread) -----------------------------------------------------
 // Contiguous `bytes` from global to shared; completion adds `bytes` to `bar`'s
 // transaction count.  The streaming form marks the lines evict-first in L2
@@ -105,16 +99,8 @@ __device__ __forceinline__ void copy_tile_1d_stream(void* smem_dst, const void* 
                  :: "r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy) : "memory");
 }
 
-// Tiled 2-D tensor-map copy: box at element coordinates (x, y); x * element size
+// Tiled 4-D tensor-map copy: box at element coordinates (x, y, z, w); x * element size
 // must be a multiple of 16 bytes.
-__device__ __forceinline__ void copy_tile_2d(void* smem_dst, const void* tensor_map, int x, int y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 :: "r"(smem_addr(smem_dst)), "l"(tensor_map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void copy_tile_3d(void* smem_dst, const void* tensor_map, int x, int y, int z, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-                 :: "r"(smem_addr(smem_dst)), "l"(tensor_map), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(z) : "memory");
-}
 __device__ __forceinline__ void copy_tile_4d(void* smem_dst, const void* tensor_map, int x, int y, int z, int w, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                  :: "r"(smem_addr(smem_dst)), "l"(tensor_map), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");

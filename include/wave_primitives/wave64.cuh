@@ -171,6 +171,39 @@ __device__ __forceinline__ T lane_group_reduce(T v, Op op) {
 }
 
 // ---------------------------------------------------------------------------
+// The reference's PORTABLE reduction order (wave_reduce.hpp:40-63): six steps
+// v[i] = op(v[i], v[i + o]) with o = 32, 16, ..., 1, result on element 0, i.e.
+// elements (i, i + 32) meet first.  Its 16-bit overloads prescribe this order
+// in fp32, so the 16-bit sums use it to agree bit for bit.
+//
+// lane_reduce_shfl_down_order<64>: ONE lane holds the whole segment; the tree
+// runs in registers with no cross-lane traffic.
+// pair_reduce_shfl_down_order: the segment is a pair per lane (elements 2l,
+// 2l+1).  Elements i and i + 32 sit in lanes l and l + 16, then l and l + 8, ...
+// so the first five levels are xor butterflies (masks 16, 8, 4, 2, 1) on both
+// elements and the last level is a (op) b inside the lane; op is commutative, so
+// both partners compute the same bits and every lane ends with the result.
+// ---------------------------------------------------------------------------
+template <int N, typename T, typename Op>
+__device__ __forceinline__ T lane_reduce_shfl_down_order(T (&v)[N], Op op) {
+    #pragma unroll
+    for (int o = N / 2; o > 0; o >>= 1) {
+        #pragma unroll
+        for (int i = 0; i < o; ++i) v[i] = op(v[i], v[i + o]);
+    }
+    return v[0];
+}
+template <typename T, typename Op>
+__device__ __forceinline__ T pair_reduce_shfl_down_order(T a, T b, Op op) {
+    #pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        a = op(a, detail::shfl_xor(a, m));
+        b = op(b, detail::shfl_xor(b, m));
+    }
+    return op(a, b);
+}
+
+// ---------------------------------------------------------------------------
 // Kogge-Stone inclusive scan over rows of ROW consecutive elements, VEC per
 // lane.  Step with offset o: x[i] = op(x[i], i-o inside the row ? x[i-o] : id).
 // This is the association of the reference's row_shr cascade (ROW = 16,
@@ -370,6 +403,47 @@ template <typename T> __device__ __forceinline__ T scan_exclusive_sum(T v) {
 
 #ifndef WAVE64_HOST_EMULATION
 // ===========================================================================
+// Vote / predicate operations and bitwise reductions (wave_ballot.hpp:23-75,
+// wave_reduce.hpp reduce_and / reduce_or).  A wave64 ballot is 64 bits: with a
+// pair per lane, bit 2l is lane l's first predicate and bit 2l+1 its second.
+// The one-argument forms are the 32-lane meaning (upper 32 bits zero), as the
+// reference defines them on a 32-wide machine.
+// ===========================================================================
+using mask_t = unsigned long long;
+__device__ __forceinline__ mask_t activemask() { return mask_t(__activemask()); }
+__device__ __forceinline__ mask_t ballot(int predicate) { return mask_t(__ballot_sync(kFullMask, predicate)); }
+__device__ __forceinline__ mask_t ballot(int pa, int pb) {
+    const unsigned ea = __ballot_sync(kFullMask, pa), eb = __ballot_sync(kFullMask, pb);
+    // interleave: bit l of ea -> bit 2l, bit l of eb -> bit 2l + 1
+    auto spread = [](unsigned x) {
+        mask_t v = x;
+        v = (v | (v << 16)) & 0x0000ffff0000ffffull;
+        v = (v | (v << 8))  & 0x00ff00ff00ff00ffull;
+        v = (v | (v << 4))  & 0x0f0f0f0f0f0f0f0full;
+        v = (v | (v << 2))  & 0x3333333333333333ull;
+        v = (v | (v << 1))  & 0x5555555555555555ull;
+        return v;
+    };
+    return spread(ea) | (spread(eb) << 1);
+}
+__device__ __forceinline__ int any(int predicate) { return __any_sync(kFullMask, predicate); }
+__device__ __forceinline__ int all(int predicate) { return __all_sync(kFullMask, predicate); }
+__device__ __forceinline__ int any(int pa, int pb) { return __any_sync(kFullMask, pa || pb); }
+__device__ __forceinline__ int all(int pa, int pb) { return __all_sync(kFullMask, pa && pb); }
+__device__ __forceinline__ int popcount(int predicate) { return __popc(__ballot_sync(kFullMask, predicate)); }
+__device__ __forceinline__ int popcount(int pa, int pb) { return __popc(__ballot_sync(kFullMask, pa)) + __popc(__ballot_sync(kFullMask, pb)); }
+// bits of the elements before this lane's first element (wave64: 2 * lane of them)
+__device__ __forceinline__ mask_t lane_mask_lt() { const unsigned l = lane_id(); return l == 0 ? 0ull : ((1ull << l) - 1ull); }
+__device__ __forceinline__ mask_t lane_mask_le() { const unsigned l = lane_id(); return (l >= 63u) ? ~0ull : ((1ull << (l + 1)) - 1ull); }
+// bitwise reductions over the wave (redux.sync), result on every lane
+__device__ __forceinline__ unsigned reduce_and(unsigned v) { return __reduce_and_sync(kFullMask, v); }
+__device__ __forceinline__ unsigned reduce_or(unsigned v)  { return __reduce_or_sync(kFullMask, v); }
+__device__ __forceinline__ unsigned reduce_and(unsigned a, unsigned b) { return __reduce_and_sync(kFullMask, a & b); }
+__device__ __forceinline__ unsigned reduce_or(unsigned a, unsigned b)  { return __reduce_or_sync(kFullMask, a | b); }
+#endif
+
+#ifndef WAVE64_HOST_EMULATION
+// ===========================================================================
 // 16-bit inputs with fp32 accumulation (wave_reduce.hpp:48-63, wave_scan.hpp:52-74).
 // The reference converts each lane's value to float, combines in float and
 // converts back; these overloads take the lane's adjacent pair and return the
@@ -381,7 +455,8 @@ template <typename N> __device__ __forceinline__ N from_f32(float f);
 template <> __device__ __forceinline__ __half        from_f32<__half>(float f)        { return __float2half_rn(f); }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float f) { return __float2bfloat16_rn(f); }
 
-template <typename N> __device__ __forceinline__ float reduce_sum_f32(N a, N b) { return dpp::reduce_sum(to_f32(a), to_f32(b)); }
+// sum: the portable order (i, i + 32 first) the reference's 16-bit overloads use; max / min do not depend on the order
+template <typename N> __device__ __forceinline__ float reduce_sum_f32(N a, N b) { return pair_reduce_shfl_down_order(to_f32(a), to_f32(b), SumOp{}); }
 template <typename N> __device__ __forceinline__ float reduce_max_f32(N a, N b) { return dpp::reduce_max(to_f32(a), to_f32(b)); }
 template <typename N> __device__ __forceinline__ float reduce_min_f32(N a, N b) { return dpp::reduce_min(to_f32(a), to_f32(b)); }
 

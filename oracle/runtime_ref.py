@@ -8,10 +8,13 @@ cdna3-prims/include/cdna3/runtime/forward.hpp (RMSNorm :34-56, RoPE :135-148, Si
 rocblas_gemm.hpp:112-209: activations are cast to the 16-bit type, products accumulate in
 fp32, Q/K/V come out 16-bit, O-proj / gate / up / down come out fp32.
 
-Parity of this file is UNPINNED against the reference: the reference validates its
-runtime only against HuggingFace artefacts (exported weights, ref_tokens.txt,
-ref_logits0.bin) that are not available offline.  The attention inside it is the pinned
-oracle (cpu_prefill / cpu_decode).
+Pinned the way the reference pins its own runtime (cdna3-prims/tests/validate_runtime.hip:
+67-86, diag_logits.hip:23-66): against HuggingFace outputs on an exported model.  The
+checkpoints the reference used are not available offline, so tests/golden/tiny_llama holds a
+tiny random-init Llama exported by the reference's own export_model.py together with
+HuggingFace's first-step logits and greedy tokens for it (tests/golden/make_runtime_golden.py);
+tests/test_runtime_golden.py checks this file against them.  The attention inside it is the
+pinned oracle (cpu_prefill / cpu_decode).
 
 Two deliberate differences from the reference, shared with the CUDA session so that the
 two stay comparable: the final norm's output is cast to 16-bit before lm_head (the
@@ -43,6 +46,32 @@ def make_weights(cfg: dict, seed: int, kind: str = "bf16", std: float = 0.02, bi
             L.update({"bq": w(qd), "bk": w(kvd), "bv": w(kvd)})
         layers.append(L)
     return {"embed_tokens": w(V, H), "lm_head": w(V, H), "final_norm": np.ones(H, np.float32), "layers": layers}
+
+
+def load_export(model_dir: str):
+    """A model directory in the reference's export format (cdna3-prims/runtime/export_model.py:
+    meta.json + one raw fp16 .bin per tensor) -> (cfg, weights) as make_weights returns them."""
+    import json
+    import os
+    meta = json.load(open(os.path.join(model_dir, "meta.json")))
+    cfg = {k: meta[k] for k in ("n_layers", "hidden", "n_heads", "n_kv_heads", "head_dim", "ffn_dim", "vocab_size")}
+    cfg["rope_theta"] = float(meta.get("rope_theta", 10000.0))
+    H, F, D = cfg["hidden"], cfg["ffn_dim"], cfg["head_dim"]
+    qd, kvd, V = cfg["n_heads"] * D, cfg["n_kv_heads"] * D, cfg["vocab_size"]
+
+    def t(name, *shape):
+        return np.fromfile(os.path.join(model_dir, name + ".bin"), dtype=np.float16).astype(np.float32).reshape(shape)
+
+    layers = []
+    for i in range(cfg["n_layers"]):
+        p = f"layer_{i}_"
+        L = {"Wq": t(p + "q_proj", qd, H), "Wk": t(p + "k_proj", kvd, H), "Wv": t(p + "v_proj", kvd, H), "Wo": t(p + "o_proj", H, qd),
+             "Wgate": t(p + "gate_proj", F, H), "Wup": t(p + "up_proj", F, H), "Wdown": t(p + "down_proj", H, F),
+             "norm_attn": t(p + "norm_attn", H), "norm_mlp": t(p + "norm_mlp", H)}
+        if meta.get("qkv_bias"):
+            L.update({"bq": t(p + "q_bias", qd), "bk": t(p + "k_bias", kvd), "bv": t(p + "v_bias", kvd)})
+        layers.append(L)
+    return cfg, {"embed_tokens": t("embed_tokens", V, H), "lm_head": t("lm_head", V, H), "final_norm": t("final_norm", H), "layers": layers}
 
 
 def rope_table(cfg: dict, max_seq: int):

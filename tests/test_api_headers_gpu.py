@@ -1,0 +1,48 @@
+"""The device-level facade a caller of the reference compiles against -- <cdna3/cdna3.hpp>,
+cdna3::ex::row_softmax_lane / online_softmax_step (cdna3-prims/examples/fused_softmax.hpp:26-48)
+and the per-thread asynchronous copy API dme::copy_tile_1d_stream / AsyncTile2D
+(research/dme-abstraction/include/dme/dme_copy.hpp:133-160, tensor_prefetch.hpp:151-196) -- run
+on the GPU by kernels that only include those headers (csrc/api_probe.cu), through the C ABI."""
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+def softmax64(x):
+    x = x.astype(np.float64)
+    e = np.exp(x - x.max(axis=-1, keepdims=True))
+    return e / e.sum(axis=-1, keepdims=True)
+
+
+@pytest.mark.parametrize("width,which", [(64, 0), (32, 1)])
+def test_row_softmax_lane(b200p, torch_cuda, width, which):
+    torch = torch_cuda
+    rows = 1237
+    x = (np.random.default_rng(width).standard_normal((rows, width)) * 3).astype(np.float32)
+    got = b200p.api_probe(which, torch.from_numpy(x).cuda(), rows).cpu().numpy().reshape(rows, width)
+    assert np.abs(got - softmax64(x)).max() < 1e-6
+    assert np.abs(got.sum(axis=1) - 1).max() < 1e-5
+
+
+def test_online_softmax_step_streams_to_the_same_result(b200p, torch_cuda):
+    torch = torch_cuda
+    rows, tiles = 515, 7
+    x = (np.random.default_rng(1).standard_normal((rows, tiles * 64)) * 4).astype(np.float32)
+    got = b200p.api_probe(2, torch.from_numpy(x).cuda(), rows, tiles, out_elems=rows * 3).cpu().numpy().reshape(rows, 3)
+    m = x.max(axis=1).astype(np.float64)
+    l = np.exp(x.astype(np.float64) - m[:, None]).sum(axis=1)
+    assert np.array_equal(got[:, 0], x.max(axis=1))
+    assert np.abs(got[:, 1] / l - 1).max() < 1e-5               # the running denominator
+    assert np.abs(got[:, 2] / l - 1).max() < 1e-5               # an accumulator rescaled by the returned factors
+
+
+def test_async_tile_ping_pong_and_tile_1d(b200p, torch_cuda):
+    torch = torch_cuda
+    tiles = 9
+    h = torch.randn(tiles, 16 * 64, device="cuda").half()
+    got = b200p.api_probe(3, h, 1, tiles).view(tiles, -1)
+    assert torch.equal(got, 2 * h.float())
+    f = torch.randn(11, 256, device="cuda")
+    got = b200p.api_probe(4, f, 1, 11).view(11, 256)
+    assert torch.equal(got, f + 1)

@@ -91,8 +91,44 @@ def test_steps_agree_with_each_other(b200p, torch_cuda):
     assert (a.float() - b.float()).abs().max().item() < 1e-3
 
 
+@pytest.mark.parametrize("variant", ["naive", "dpp"])
+@pytest.mark.parametrize("bc", [64, 128, 256])
+@pytest.mark.parametrize("S,D", [(512, 64), (200, 64), (333, 128), (64, 64), (1, 64)])
+def test_fp32_row_kernels_ragged_and_wide_tiles(b200p, torch_cuda, variant, bc, S, D):
+    """The fp32-I/O kernels with one query row per block: Bc = 64 / 128 / 256 keys per tile over
+    Bc/64 waves (two-phase block reduction, kernels/fa_dpp.hip:96-155) and any seq_len, keys past
+    the end padded (kernels/fa_naive.hip:158-169,233); against cpu_attention_ref, max|delta| < 1e-4."""
+    torch = torch_cuda
+    B, H = 2, 3
+    n = B * H * S * D
+    a = orc.gen_normal_mt19937(42, 0.0, 0.3, 3 * n)
+    q, k, v = a[:n], a[n:2 * n], a[2 * n:]
+    scale = 1.0 / np.sqrt(D)
+    ref = orc.cpu_attention_ref_heads(q, k, v, B * H, S, D, scale, threads=8).reshape(B, H, S, D)
+    got = b200p.fa_rows_f32(variant, bc, dev(torch, q.reshape(B, H, S, D), "f32"), dev(torch, k.reshape(B, H, S, D), "f32"),
+                            dev(torch, v.reshape(B, H, S, D), "f32"), scale=scale).cpu().numpy()
+    assert np.isfinite(got).all()
+    assert np.abs(got - ref).max() < 1e-4
+
+
+@pytest.mark.parametrize("step", STEPS[:3])
+def test_fp32_steps_accept_ragged_lengths(b200p, torch_cuda, step):
+    """b200p_fa_step with fp32 I/O and a length off the Br = 16 / Bc = 64 tiling takes the row kernels."""
+    torch = torch_cuda
+    D, S, H = 64, 203, 4
+    rng = np.random.default_rng(0xB201)
+    q, k, v = (rng.uniform(-1, 1, (1, H, S, D)).astype(np.float32) for _ in range(3))
+    ref = orc.cpu_prefill(q, k, v, D, S, S, H, H, 1, 0, threads=8)
+    got = b200p.fa_step(step, dev(torch, q, "f32"), dev(torch, k, "f32"), dev(torch, v, "f32"))
+    assert np.abs(got.cpu().numpy() - ref).max() < 1e-4
+
+
 def test_argument_errors(b200p, torch_cuda):
     torch = torch_cuda
+    Q = torch.zeros(1, 2, 100, 64, device="cuda")
+    with pytest.raises(b200p.B200PError) as e:
+        b200p.fa_rows_f32("dpp", 96, Q, Q, Q)               # Bc must be 64, 128 or 256
+    assert e.value.status == -3
     Q = torch.zeros(1, 2, 100, 64, device="cuda", dtype=torch.float16)
     with pytest.raises(b200p.B200PError) as e:
         b200p.fa_step("dpp", Q, Q, Q)                       # seq not a multiple of the tile

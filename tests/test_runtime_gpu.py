@@ -1,6 +1,6 @@
 """The small LLM runtime (CUDA session through the C ABI) against the numpy restatement
-of the reference's Session (oracle/runtime_ref.py).  Random-init weights stand in for the
-HF checkpoint.  Both sides round to 16 bits at the same places, so logits differ only by
+of the reference's Session (oracle/runtime_ref.py, pinned to HuggingFace outputs by
+tests/test_runtime_golden.py).  Random-init weights stand in for the HF checkpoint.  Both sides round to 16 bits at the same places, so logits differ only by
 fp32 accumulation order and exp implementations, plus the occasional 1-ulp flip of a
 16-bit intermediate.  Gates: max|delta logits| < 5% of the logits' standard deviation and
 cosine > 0.9999 on the first decode step and on teacher-forced steps; teacher-forced argmax
@@ -118,6 +118,62 @@ def test_generate_graph_replay_equals_launched_steps(b200p, torch_cuda):
             assert np.array_equal(toks[:, s_], nxt), s_
             if s_ + 1 < new:
                 lg = sess.step_logits(nxt)
+    assert b200p.device_status() == 0
+    sess.close()
+
+
+# BASELINE config 5's dimensions (the Llama-style decoder of the reference's runtime benchmark)
+C5 = dict(hidden=2048, n_heads=32, n_kv_heads=4, head_dim=64, ffn_dim=5632, vocab_size=32000, rope_theta=10000.0)
+
+
+def test_config5_dimensions_against_the_oracle(b200p, torch_cuda):
+    """Two layers at the full config-5 widths, batch 2, a 512-token prompt and 8 teacher-forced steps against
+    the numpy restatement of the reference Session (itself pinned to HuggingFace on the exported tiny model)."""
+    torch = torch_cuda
+    cfg = dict(C5, n_layers=2)
+    batch, T, steps = 2, 512, 8
+    w = rr.make_weights(cfg, seed=5, kind="bf16", std=0.02)
+    ref = rr.RefSession(cfg, w, T + steps, batch, "bf16")
+    sess = b200p.Session(cfg, to_device(torch, w, "bf16"), T + steps, batch)
+    ids = np.random.default_rng(0xB205).integers(0, cfg["vocab_size"], (batch, T)).astype(np.int32)
+    g, r = sess.prefill_logits(ids), ref.prefill_logits(ids)
+    tol = check_logits(g, r)
+    for _ in range(steps):
+        nxt = ref.argmax(r)
+        srt = np.sort(orc.round_to(r, "bf16"), axis=-1)
+        clear = (srt[:, -1] - srt[:, -2]) > 2 * tol
+        assert (np.argmax(orc.round_to(g, "bf16"), axis=-1)[clear] == nxt[clear]).all()
+        g, r = sess.step_logits(nxt), ref.step_logits(nxt)
+        check_logits(g, r)
+    assert b200p.device_status() == 0
+    sess.close()
+
+
+def test_config5_full_depth_generate_equals_stepwise(b200p, torch_cuda):
+    """All 22 layers at config 5 (2.2 GB of weights): generate() -- device-side greedy loop, captured step
+    graph -- gives exactly the tokens of the host-driven prefill_logits / step_logits loop
+    (cdna3-prims/include/cdna3/runtime/session.hpp:263-296)."""
+    torch = torch_cuda
+    cfg = dict(C5, n_layers=22)
+    batch, T, new = 2, 512, 10
+    g = torch.Generator(device="cuda"); g.manual_seed(0xB205)
+    H, F, D = cfg["hidden"], cfg["ffn_dim"], cfg["head_dim"]
+    qd, kvd = cfg["n_heads"] * D, cfg["n_kv_heads"] * D
+    wt = lambda *shape: (torch.randn(shape, device="cuda", generator=g) * 0.02).bfloat16()
+    ones = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    layers = [{"Wq": wt(qd, H), "Wk": wt(kvd, H), "Wv": wt(kvd, H), "Wo": wt(H, qd), "Wgate": wt(F, H), "Wup": wt(F, H),
+               "Wdown": wt(H, F), "norm_attn": ones, "norm_mlp": ones} for _ in range(cfg["n_layers"])]
+    weights = {"embed_tokens": wt(cfg["vocab_size"], H), "lm_head": wt(cfg["vocab_size"], H), "final_norm": ones, "layers": layers}
+    sess = b200p.Session(cfg, weights, T + new, batch)
+    ids = np.random.default_rng(7).integers(0, cfg["vocab_size"], (batch, T)).astype(np.int32)
+    toks, _ = sess.generate(ids, new)
+    assert sess.graph_replays == new - 2
+    lg = sess.prefill_logits(ids)
+    for s_ in range(new):
+        nxt = np.argmax(orc.round_to(lg, "bf16"), axis=-1).astype(np.int32)
+        assert np.array_equal(toks[:, s_], nxt), s_
+        if s_ + 1 < new:
+            lg = sess.step_logits(nxt)
     assert b200p.device_status() == 0
     sess.close()
 
