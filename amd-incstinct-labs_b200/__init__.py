@@ -35,6 +35,8 @@ SYMBOLS = {
     "b200p_wave_probe_n": (_i, [_i, _i, _i, _vp, _vp, _i, _vp]),
     "b200p_wave_vote_probe": (_i, [_vp, _vp, _vp]),
     "b200p_api_probe": (_i, [_i, _vp, _vp, _i, _i, _vp]),
+    "b200p_wave_reduce_loop": (_i, [_i, _i, _i, _vp, _vp, _i, _i, _vp]),
+    "b200p_row_op": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _i, C.c_float, _vp]),
     "b200p_fa_rows_f32": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, C.c_float, _vp]),
     "b200p_model_read_meta": (_i, [C.c_char_p, _vp, _vp, _vp]),
     "b200p_model_load": (_vp, [C.c_char_p, _vp]),
@@ -62,6 +64,8 @@ SYMBOLS = {
     "b200p_skinny_gemm": (_i, [_i, _i, _i, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.c_float, _vp]),
     "b200p_session_kv_len": (_i, [_vp]),
     "b200p_session_gemm_calls": (C.c_ulonglong, [_vp]),
+    "b200p_session_blas_calls": (C.c_ulonglong, [_vp]),
+    "b200p_gemm_16": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp]),
     "b200p_session_graph_replays": (C.c_ulonglong, [_vp]),
     "b200p_fa_step": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.c_float, _vp]),
 }
@@ -434,6 +438,33 @@ def fa_step(step: str, Q, K, V, scale: float = 0.0, out=None):
     return out
 
 
+def wave_reduce_loop(x, op: str, reps: int, backend: str = "primitives", out=None):
+    """The reference's register-resident reduce benchmark loop over x.numel() / 64 waves (a multiple of 8);
+    backend "primitives" (wave::dpp::reduce_*) or "portable" (shuffle-down loop).  Returns one value per wave."""
+    import torch
+    _dev(x, "x")
+    waves = x.numel() // 64
+    if out is None:
+        out = torch.empty(waves, dtype=x.dtype, device=x.device)
+    _check(lib().b200p_wave_reduce_loop(OPS[op], _dtype_code(x), {"primitives": 0, "portable": 1}[backend], x.data_ptr(),
+                                        out.data_ptr(), waves, int(reps), _stream(x)), "wave_reduce_loop")
+    return out
+
+
+def row_op(which: str, x, gamma=None, beta=None, backend: str = "primitives", eps: float = 1e-5, out=None):
+    """LayerNorm ("layernorm", needs gamma and beta) or softmax ("softmax") over the rows of x [rows, 64 | 512] fp32,
+    one warp per row, on the wave primitives or on the portable shuffle loop."""
+    import torch
+    _dev(x, "x")
+    rows, cols = x.shape
+    if out is None:
+        out = torch.empty_like(x)
+    _check(lib().b200p_row_op({"layernorm": 0, "softmax": 1}[which], {"primitives": 0, "portable": 1}[backend], cols, x.data_ptr(),
+                              gamma.data_ptr() if gamma is not None else None, beta.data_ptr() if beta is not None else None,
+                              out.data_ptr(), rows, float(eps), _stream(x)), "row_op")
+    return out
+
+
 def fa_rows_f32(variant: str, bc: int, Q, K, V, scale: float = 0.0, out=None):
     """The reference's fp32-I/O kernels (one query row per block, bc keys per tile, any seq_len):
     variant "naive" or "dpp"; Q,K,V [batch, heads, seq, D] fp32."""
@@ -515,6 +546,20 @@ class Model:
             self._h = None
 
     __del__ = close
+
+
+def gemm_16(A, W, out, epilogue: str = "store16"):
+    """out[M, N] = A[M, K] . W[N, K]^T on the tensor cores; epilogue store16 / store32 / acc32 (out += product) /
+    silu16 (W = [gate; up] with 2N rows, out = SiLU(gate) * up).  A, W 16-bit CUDA tensors with contiguous rows."""
+    epi = {"store16": 0, "acc32": 1, "store32": 2, "silu16": 3}[epilogue]
+    for t, n in ((A, "A"), (W, "W"), (out, "out")):
+        if not t.is_cuda or t.stride(-1) != 1:
+            raise ValueError(f"{n} must be a CUDA tensor with contiguous rows: there is no CPU path")
+    M, K = A.shape
+    N = W.shape[0] // (2 if epi == 3 else 1)
+    _check(lib().b200p_gemm_16(_dtype_code(A), epi, A.data_ptr(), W.data_ptr(), out.data_ptr(), M, N, K,
+                               A.stride(0), W.stride(0), out.stride(0), _stream(A)), "gemm_16")
+    return out
 
 
 class Session:
@@ -607,6 +652,10 @@ class Session:
     @property
     def gemm_calls(self) -> int:
         return int(lib().b200p_session_gemm_calls(self._h))
+
+    @property
+    def blas_calls(self) -> int:
+        return int(lib().b200p_session_blas_calls(self._h))
 
     @property
     def graph_replays(self) -> int:

@@ -15,7 +15,7 @@ std::atomic<unsigned> g_tuning_epoch{0};
 struct KnobInit { KnobInit() { for (auto& k : g_knobs) k.store(-1); } } g_knob_init;
 const char* const kKnobNames[KNOB_COUNT] = {
     "seg_vec_bytes", "seg_ctas_per_sm", "scan_fp_exact", "decode_splits", "decode_fused_combine", "decode_variant", "prefill_variant",
-    "runtime_graph", "runtime_pdl", "runtime_rope_fused", "runtime_skinny", "scan16_lane",
+    "runtime_graph", "runtime_pdl", "runtime_rope_fused", "runtime_skinny", "scan16_lane", "runtime_gemm", "gemm_tile_n",
 };
 constexpr int kMaxDevices = 64;
 std::atomic<int> g_sms[kMaxDevices];

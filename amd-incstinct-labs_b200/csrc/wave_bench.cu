@@ -1,0 +1,159 @@
+// ---------------------------------------------------------------------------
+// wave_bench.cu -- kernels that measure the DEVICE-level wave API in the
+// reference's own terms, and two small "real kernels" built on it.
+//
+// 1. Register-resident reduce loop (research/wave-primitives/benchmarks/
+//    bench_reduce_dpp_types.hip:29-45): every wave reduces its 64 values kReps
+//    times, feeding the result back into the inputs so that nothing can be
+//    hoisted; no memory traffic inside the loop.  A wave is one warp holding a
+//    pair per lane.  Backends: 0 = wave::dpp::reduce_* (xor butterfly, redux.sync
+//    where the type has it), 1 = the portable shfl_down loop + broadcast the
+//    reference benchmarks against (wave_reduce.hpp:40-46).
+// 2. LayerNorm and softmax over rows of 64 * E elements, one warp per row, E pairs
+//    per lane (research/wave-primitives/benchmarks/bench_layernorm.hip:47-96,
+//    bench_softmax.hip): two row reductions each, with the same two backends.
+// ---------------------------------------------------------------------------
+#include "common.cuh"
+#include "wave_primitives/wave64.cuh"
+
+namespace b200p {
+namespace {
+
+template <typename T, typename Op>
+__device__ __forceinline__ T portable_pair_reduce_bcast(T a, T b, Op op) {
+    T v = op(a, b);
+    #pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = op(v, __shfl_down_sync(0xffffffffu, v, o));
+    return __shfl_sync(0xffffffffu, v, 0);
+}
+
+template <typename T, int OP, int BACKEND>
+__global__ void __launch_bounds__(256)
+wave_reduce_loop_kernel(const T* __restrict__ in, T* __restrict__ out, int reps) {
+    const size_t wave_i = size_t(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    const unsigned l = threadIdx.x % 32;
+    T a = in[wave_i * 64 + 2 * l], b = in[wave_i * 64 + 2 * l + 1];
+    T acc = T(0);
+    #pragma unroll 1
+    for (int r = 0; r < reps; ++r) {
+        T s;
+        if (BACKEND == 0) {
+            if (OP == 0)      s = wave::dpp::reduce_sum(a, b);
+            else if (OP == 1) s = wave::dpp::reduce_max(a, b);
+            else              s = wave::dpp::reduce_min(a, b);
+        } else {
+            if (OP == 0)      s = portable_pair_reduce_bcast(a, b, wave::SumOp{});
+            else if (OP == 1) s = portable_pair_reduce_bcast(a, b, wave::MaxOp{});
+            else              s = portable_pair_reduce_bcast(a, b, wave::MinOp{});
+        }
+        acc = acc + s;
+        // per-lane perturbation: the next round's inputs depend on this round's result
+        a = s + T(2 * l) + T(1);
+        b = s + T(2 * l + 1) + T(1);
+    }
+    if (l == 31) out[wave_i] = acc;
+}
+
+template <typename T, int BACKEND>
+int launch_loop(int op, const void* in, void* out, int waves, int reps, cudaStream_t st) {
+    const int grid = waves / 8;
+    const T* i = static_cast<const T*>(in); T* o = static_cast<T*>(out);
+    switch (op) {
+        case B200P_SUM: wave_reduce_loop_kernel<T, 0, BACKEND><<<grid, 256, 0, st>>>(i, o, reps); break;
+        case B200P_MAX: wave_reduce_loop_kernel<T, 1, BACKEND><<<grid, 256, 0, st>>>(i, o, reps); break;
+        default:        wave_reduce_loop_kernel<T, 2, BACKEND><<<grid, 256, 0, st>>>(i, o, reps); break;
+    }
+    return launched();
+}
+
+template <int BACKEND> __device__ __forceinline__ float row_sum(float a, float b) {
+    return BACKEND == 0 ? wave::dpp::reduce_sum_bcast(a, b) : portable_pair_reduce_bcast(a, b, wave::SumOp{});
+}
+template <int BACKEND> __device__ __forceinline__ float row_max(float a, float b) {
+    return BACKEND == 0 ? wave::dpp::reduce_max_bcast(a, b) : portable_pair_reduce_bcast(a, b, wave::MaxOp{});
+}
+
+// which 0: y = (x - mean) / sqrt(var + eps) * gamma + beta;  which 1: y = softmax(x).  Row = 64 * E floats; lane l holds
+// the float2 at columns 64 e + 2 l (e = 0 .. E-1), so a warp reads whole 256-byte runs.
+template <int E, int BACKEND>
+__global__ void __launch_bounds__(256)
+row_op_kernel(int which, const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
+              float* __restrict__ out, int rows, float eps) {
+    const int row = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+    if (row >= rows) return;
+    const unsigned l = threadIdx.x % 32;
+    constexpr int COLS = 64 * E;
+    const float2* xr = reinterpret_cast<const float2*>(x + size_t(row) * COLS);
+    float2 v[E];
+    #pragma unroll
+    for (int e = 0; e < E; ++e) v[e] = xr[e * 32 + l];
+    float2* orow = reinterpret_cast<float2*>(out + size_t(row) * COLS);
+    if (which == 0) {
+        float sa = 0.f, sb = 0.f;
+        #pragma unroll
+        for (int e = 0; e < E; ++e) { sa += v[e].x; sb += v[e].y; }
+        const float mean = row_sum<BACKEND>(sa, sb) * (1.f / COLS);
+        float qa = 0.f, qb = 0.f;
+        #pragma unroll
+        for (int e = 0; e < E; ++e) { const float dx = v[e].x - mean, dy = v[e].y - mean; qa += dx * dx; qb += dy * dy; }
+        const float inv = rsqrtf(row_sum<BACKEND>(qa, qb) * (1.f / COLS) + eps);
+        #pragma unroll
+        for (int e = 0; e < E; ++e) {
+            const float2 g = reinterpret_cast<const float2*>(gamma)[e * 32 + l], bt = reinterpret_cast<const float2*>(beta)[e * 32 + l];
+            orow[e * 32 + l] = make_float2((v[e].x - mean) * inv * g.x + bt.x, (v[e].y - mean) * inv * g.y + bt.y);
+        }
+    } else {
+        float ma = v[0].x, mb = v[0].y;
+        #pragma unroll
+        for (int e = 1; e < E; ++e) { ma = fmaxf(ma, v[e].x); mb = fmaxf(mb, v[e].y); }
+        const float m = row_max<BACKEND>(ma, mb);
+        float sa = 0.f, sb = 0.f;
+        #pragma unroll
+        for (int e = 0; e < E; ++e) { v[e].x = __expf(v[e].x - m); v[e].y = __expf(v[e].y - m); sa += v[e].x; sb += v[e].y; }
+        const float inv = 1.f / row_sum<BACKEND>(sa, sb);
+        #pragma unroll
+        for (int e = 0; e < E; ++e) orow[e * 32 + l] = make_float2(v[e].x * inv, v[e].y * inv);
+    }
+}
+
+template <int E>
+int launch_row(int which, int backend, const float* x, const float* g, const float* b, float* out, int rows, float eps, cudaStream_t st) {
+    const int grid = (rows + 7) / 8;
+    if (backend == 0) row_op_kernel<E, 0><<<grid, 256, 0, st>>>(which, x, g, b, out, rows, eps);
+    else              row_op_kernel<E, 1><<<grid, 256, 0, st>>>(which, x, g, b, out, rows, eps);
+    return launched();
+}
+
+} // namespace
+} // namespace b200p
+
+using namespace b200p;
+
+extern "C" int b200p_wave_reduce_loop(int op, int dtype, int backend, const void* in, void* out, int n_waves, int reps,
+                                      b200p_stream_t stream) {
+    if (op < B200P_SUM || op > B200P_MIN || (backend != 0 && backend != 1)) return B200P_E_OP;
+    if (dtype < B200P_F32 || dtype > B200P_I64) return B200P_E_DTYPE;
+    if (n_waves <= 0 || n_waves % 8 != 0 || reps <= 0) return B200P_E_LENGTH;
+    if (!in || !out) return B200P_E_NULL;
+    if (sm_count() <= 0) return B200P_E_NO_DEVICE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case B200P_F32: return backend == 0 ? launch_loop<float, 0>(op, in, out, n_waves, reps, st) : launch_loop<float, 1>(op, in, out, n_waves, reps, st);
+        case B200P_F64: return backend == 0 ? launch_loop<double, 0>(op, in, out, n_waves, reps, st) : launch_loop<double, 1>(op, in, out, n_waves, reps, st);
+        case B200P_I32: return backend == 0 ? launch_loop<int, 0>(op, in, out, n_waves, reps, st) : launch_loop<int, 1>(op, in, out, n_waves, reps, st);
+        default:        return backend == 0 ? launch_loop<long long, 0>(op, in, out, n_waves, reps, st) : launch_loop<long long, 1>(op, in, out, n_waves, reps, st);
+    }
+}
+
+extern "C" int b200p_row_op(int which, int backend, int cols, const float* x, const float* gamma, const float* beta, float* out,
+                            int rows, float eps, b200p_stream_t stream) {
+    if ((which != 0 && which != 1) || (backend != 0 && backend != 1)) return B200P_E_OP;
+    if (cols != 64 && cols != 512) return B200P_E_LENGTH;
+    if (rows <= 0) return B200P_E_LENGTH;
+    if (!x || !out || (which == 0 && (!gamma || !beta))) return B200P_E_NULL;
+    if (!aligned(x, 8) || !aligned(out, 8) || (which == 0 && (!aligned(gamma, 8) || !aligned(beta, 8)))) return B200P_E_ALIGN;
+    if (sm_count() <= 0) return B200P_E_NO_DEVICE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    return cols == 64 ? launch_row<1>(which, backend, x, gamma, beta, out, rows, eps, st)
+                      : launch_row<8>(which, backend, x, gamma, beta, out, rows, eps, st);
+}

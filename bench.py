@@ -10,18 +10,26 @@ K steps timed with CUDA events on the launching stream between a barrier +
 synchronize on both sides; the time is the max over ranks; rank 0 prints ONE
 JSON line.
 
-Workloads (default `all`: segops is the headline line, decode and prefill ride along
-under "others", each with its own roofline, e2e and cpu_baseline)
+Workloads (default `all`: prefill is the headline line, the others ride along under
+"others", each with its own roofline, e2e and cpu_baseline)
+  prefill      causal prefill, batch 8, 32 heads, seq 4096, D 128, bf16.  Tensor-bound.
+               N > 1: every rank its own (batch, head) units (weak).
+  decode       GQA decode, batch 64, 32 q / 8 kv heads, D 128, 8192 cached keys, bf16.
+               HBM-bound.  N > 1: every rank its own (batch, kv-head) units (weak).
   segops       segmented wave64 reduce + inclusive-scan sweep over 2^26 elements per
                dtype: reduce {f32,f64,i32,i64} x {sum,max,min}, reduce {f16,bf16} sum
                (fp32 accumulation), scan-sum {f32,f64,i32,i64,f16,bf16}.  HBM-bound.
                N > 1: every rank sweeps its own 2^26-element shard (weak scaling).
-  decode       GQA decode, batch 64, 32 q / 8 kv heads, D 128, 8192 cached keys, bf16.
-               HBM-bound.  N > 1: every rank its own (batch, kv-head) units (weak).
-  prefill      causal prefill, batch 8, 32 heads, seq 4096, D 128, bf16.  Tensor-bound.
-               N > 1: every rank its own (batch, head) units (weak).
-  decode_long  the 131072-key decode with the KV sequence split across the ranks and
-               one NCCL all-gather of (O, lse) per step (strong scaling).
+  decode_long  the 131072-key decode with the KV sequence split across the ranks and the
+               (O, lse) partials exchanged once per step (strong scaling; N = 1 holds the
+               whole sequence).  At N > 1 both forms of the exchange are timed.
+  runtime      the 22-layer Llama-style decoder: 512-token prompt + 128 greedy tokens,
+               2 sequences per GPU.
+  fa_steps     the FA2 build-order steps at the reference's validation shape (batch 1,
+               8 heads, seq 512, D 64): four steps in fp16, three in fp32.
+  wave_api     the device-level wave API in the reference's own terms: LayerNorm / softmax
+               rows on the primitives vs the portable shuffle loop, and the register-resident
+               reduce loop (elements per second).  Secondary, labelled.
 
 --impl reference times the CPU statement of the same path (the oracle) on the
 host cores, on a bounded sample, in the same metric.
@@ -59,7 +67,7 @@ class ClockSampler:
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
                0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, index: int, period: float = 0.01):
+    def __init__(self, index: int, period: float = 0.002):
         self.index, self.period = index, period
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -172,7 +180,6 @@ class SegopsSweep:
                 self.out.append(torch.empty(self.n // 64, dtype=odt, device=device))
             else:
                 self.out.append(torch.empty_like(x))
-        self.host_out = [torch.empty(o.shape, dtype=o.dtype).pin_memory() for o in self.out]
         torch.cuda.synchronize()
 
     def step(self, events=None):
@@ -199,22 +206,24 @@ class SegopsSweep:
         else:
             self.pkg.segscan(x, op, out=self.out[i])
 
-    def step_e2e(self):
-        """The same sweep through the public API from HOST buffers: H2D of every
-        input from pinned memory, the launches, D2H of every result."""
-        for k, h in self.host.items():
-            self.dev[k].copy_(h, non_blocking=True)
-        self.step()
-        for o, h in zip(self.out, self.host_out):
-            h.copy_(o, non_blocking=True)
+    def setup_e2e(self):
+        """The same sweep through the package's host-buffer entry point: one chunk per dtype,
+        uploads, kernels and downloads of successive chunks overlapped on three streams."""
+        import importlib
+        hp = importlib.import_module(self.pkg.__name__ + ".hostpipe")
+        jobs = [(kind, fn, op) for (_l, fn, kind, op, _b) in self.cases]
+        self.pipe, self.e2e_results = hp.segops_sweep_host(self.pkg, self.host, jobs)
+
+    def step_e2e(self, compute=True):
+        self.pipe.run(compute=compute)
 
     cpu_sample = 1 << 24
     cpu_sample_text = "the same sweep over 2^24 elements per dtype (1/4 of the workload)"
 
     def e2e_bytes(self):
-        h2d = sum(v.numel() * v.element_size() for v in self.host.values())
-        d2h = sum(v.numel() * v.element_size() for v in self.host_out)
-        return h2d, d2h
+        return self.pipe.bytes()
+
+    e2e_note = "host-buffer sweep (hostpipe.segops_sweep_host): per-dtype chunks, H2D / kernels / D2H on three streams"
 
     # CPU statement of the same sweep on a bounded sample
     def cpu_run(self, orc, n, threads, reps=1):
@@ -349,14 +358,18 @@ class PrefillCausal:
         if events is not None:
             e = self.torch.cuda.Event(enable_timing=True); e.record(); events.append(e)
 
-    def step_e2e(self):
-        for d, h in zip((self.Q, self.K, self.V), self.host):
-            d.copy_(h, non_blocking=True)
-        self.step()
-        self.O_host.copy_(self.O, non_blocking=True)
+    def setup_e2e(self):
+        import importlib
+        hp = importlib.import_module(self.pkg.__name__ + ".hostpipe")
+        self.pipe, self.O_host = hp.prefill_host(self.pkg, self.host[0], self.host[1], self.host[2], causal=True, Oh=self.O_host)
+
+    def step_e2e(self, compute=True):
+        self.pipe.run(compute=compute)
 
     def e2e_bytes(self):
-        return 3 * self.Q.numel() * 2, self.O.numel() * 2
+        return self.pipe.bytes()
+
+    e2e_note = "host-buffer prefill (hostpipe.prefill_host): one chunk per sequence, H2D / kernel / D2H on three streams"
 
     def cpu_run(self, orc, n, threads, reps=1):
         """n = (batch, head) units at full sequence length."""
@@ -439,6 +452,56 @@ class DecodeLong:
         self.q.copy_(self.q_host, non_blocking=True)
         self.step()
         self.o_host.copy_(self.dec.out, non_blocking=True)
+
+    def time_other_exchange(self, steps, barrier, max_over_ranks):
+        """N > 1: the same steps with the OTHER form of the (O, lse) exchange (NCCL all-gather when the timed
+        region used peer stores, and the reverse), so that one run records both.  Returns (name, ms per step)."""
+        import torch.distributed as dist
+        import importlib
+        torch = self.torch
+        if self.world == 1:
+            return None
+        other = "nccl" if self.used_exchange == "peer" else "peer"
+        sharding = importlib.import_module(self.pkg.__name__ + ".sharding")
+        try:
+            dec = sharding.LongContextDecoder(self.pkg, dist, self.B, self.NQH, self.D, torch.bfloat16, self.q.device, exchange=other)
+        except Exception as exc:                                  # no symmetric memory on this box: only NCCL exists
+            return {"exchange": other, "unavailable": str(exc)[:120]}
+        for _ in range(3):
+            dec.step(self.q, self.K, self.V, n_keys=self.len)
+        barrier()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(steps):
+            dec.step(self.q, self.K, self.V, n_keys=self.len)
+        b.record()
+        barrier()
+        ms = max_over_ranks(a.elapsed_time(b)) / steps
+        dec.check()
+        same = bool(torch.equal(dec.out, self.dec.out))
+        return {"exchange": other, "ms_per_step": ms, "GB/s": self.total_bytes / (ms * 1e-3) / 1e9, "same_bits_as_timed_exchange": same}
+
+    def parity(self):
+        """Outside the timed region: rank 0's output for two sampled sequences against a single-launch decode over
+        the whole KV sequence of those sequences, gathered from the ranks' shards -- what a single GPU would have
+        computed.  The only check the concurrent multi-GPU exchange can get (max |delta|, bf16 outputs)."""
+        import torch.distributed as dist
+        torch = self.torch
+        seqs = [0, self.B - 1]
+        if self.world == 1:
+            return None
+        rank = dist.get_rank()
+        Ks = [torch.empty((len(seqs),) + tuple(self.K.shape[1:]), dtype=self.K.dtype, device=self.K.device) for _ in range(self.world)]
+        Vs = [torch.empty_like(Ks[0]) for _ in range(self.world)]
+        dist.all_gather(Ks, self.K[seqs].contiguous())
+        dist.all_gather(Vs, self.V[seqs].contiguous())
+        out = None
+        if rank == 0:
+            Kf, Vf = torch.cat(Ks, dim=2)[:, :, :self.N].contiguous(), torch.cat(Vs, dim=2)[:, :, :self.N].contiguous()
+            ref = self.pkg.decode(self.q[seqs].contiguous(), Kf, Vf)
+            out = float((ref.float() - self.dec.out[seqs].float()).abs().max().item())
+        del Ks, Vs
+        return out
 
     def e2e_bytes(self):
         return self.q_host.numel() * 2, self.o_host.numel() * 2
@@ -531,11 +594,15 @@ class RuntimeLlama:
                 "gemm_calls_total": self.sess.gemm_calls}
 
     def cpu_run(self, orc, n, threads, reps=1):
-        """n = new tokens; one sequence, prompt 64 (bounded: the CPU statement needs seconds per prompt token block)."""
+        """n = new tokens; one sequence, prompt 64 (bounded: the CPU statement needs seconds per prompt token block).
+        One random layer's matrices serve all 22 layers: the arithmetic per token is the full model's, and drawing
+        1.1e9 normals on the host would cost more than the run it feeds."""
         import numpy as np
         from oracle import runtime_ref as rr
         if not hasattr(self, "_cpu_w"):
-            self._cpu_w = rr.make_weights(self.CFG, seed=5, kind="bf16", std=0.02)
+            one = rr.make_weights(dict(self.CFG, n_layers=1), seed=5, kind="bf16", std=0.02)
+            one["layers"] = one["layers"] * self.CFG["n_layers"]
+            self._cpu_w = one
         ids = np.random.default_rng(1).integers(0, self.CFG["vocab_size"], (1, 64))
         t0 = time.perf_counter()
         for _ in range(reps):
@@ -547,9 +614,220 @@ class RuntimeLlama:
     cpu_sample_text = "1 sequence, prompt 64 tokens + 8 new tokens (numpy restatement of the reference Session)"
 
 
-WORKLOADS = {"segops": SegopsSweep, "decode": DecodeGQA, "prefill": PrefillCausal, "decode_long": DecodeLong,
+# --------------------------------------------------------------------------------------
+# workload: the FA2 build-order steps at the reference's validation shape (BASELINE config 1)
+# --------------------------------------------------------------------------------------
+class FaSteps:
+    name = "fa_steps"
+    metric = "FA2 build-order steps at the validation shape (batch 1, 8 heads, seq 512, D 64): aggregate throughput of the 7 kernels"
+    unit = "TFLOP/s"
+    dtype = "fp16 and fp32 I/O (fp32 softmax and accumulation)"
+    bound = "tensor"
+    B, H, S, D = 1, 8, 512, 64
+    FLOPS = 4.0 * 1 * 8 * 512 * 512 * 64                         # 536 870 912, the reference's count (fa_naive.hip:336-337)
+
+    def __init__(self, n=None):
+        self.cases = [(f"fa_{st}<{dt}>", st, dt, None, self.FLOPS)
+                      for dt, steps in (("f16", ("naive", "dpp", "dme", "mfma2")), ("f32", ("naive", "dpp", "dme"))) for st in steps]
+        self.flops_per_step = self.FLOPS * len(self.cases)
+        self.bytes_per_step = self.flops_per_step
+
+    def config(self, world):
+        return {"workload": "FA2 forward steps naive/dpp/dme/mfma2 (BASELINE config 1)", "batch": self.B, "heads": self.H, "seq_len": self.S,
+                "head_dim": self.D, "causal": False, "tiles": "Br 16, Bc 64", "launches_per_step": len(self.cases),
+                "sharding": f"replicas x{world}, no collective", "flops": "4*B*H*S*S*D per kernel (the reference's convention)",
+                "l2": "working set 4 MiB (smaller than L2 by the config's definition): a 256 MB buffer is written between timed launches",
+                "protocol": "per kernel: 20 warm-up + 200 timed launches, one event pair per launch, L2 flushed in between; median and p99",
+                "inputs": "fp16: N(0,0.5) rounded, seeded; fp32: uniform[-1,1], seeded"}
+
+    def setup(self, torch, pkg, device, rank):
+        self.torch, self.pkg = torch, pkg
+        g = torch.Generator(device=device); g.manual_seed(0xB201)
+        shape = (self.B, self.H, self.S, self.D)
+        self.x16 = [(torch.randn(shape, device=device, generator=g) * 0.5).half() for _ in range(3)]
+        self.x32 = [torch.rand(shape, device=device, generator=g) * 2 - 1 for _ in range(3)]
+        self.o16, self.o32 = torch.empty_like(self.x16[0]), torch.empty_like(self.x32[0])
+        self.h32 = [t.cpu().pin_memory() for t in self.x32]
+        self.oh = torch.empty(shape, dtype=torch.float32).pin_memory()
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+        torch.cuda.synchronize()
+
+    def launch(self, i):
+        _l, st, dt, _o, _f = self.cases[i]
+        if dt == "f16":
+            self.pkg.fa_step(st, *self.x16, out=self.o16)
+        else:
+            self.pkg.fa_step(st, *self.x32, out=self.o32)
+
+    def step(self, events=None):
+        for i in range(len(self.cases)):
+            self.launch(i)
+            if events is not None:
+                e = self.torch.cuda.Event(enable_timing=True); e.record(); events.append(e)
+
+    def step_e2e(self):
+        """fp32 Q, K, V from pinned host memory, the three fp32 steps, O back."""
+        for d, h in zip(self.x32, self.h32):
+            d.copy_(h, non_blocking=True)
+        for i, c in enumerate(self.cases):
+            if c[2] == "f32":
+                self.launch(i)
+        self.oh.copy_(self.o32, non_blocking=True)
+
+    e2e_units = 3 * FLOPS
+
+    def e2e_bytes(self):
+        return 3 * self.x32[0].numel() * 4, self.o32.numel() * 4
+
+    def per_kernel(self):
+        """The reference's protocol per kernel (research/wave-primitives/benchmarks/bench_common.hpp:86-119):
+        20 warm-up + 200 timed launches; here each timed launch has its own event pair and L2 is flushed before it."""
+        torch = self.torch
+        out = []
+        for i, c in enumerate(self.cases):
+            for _ in range(20):
+                self.launch(i)
+            ts = []
+            for _ in range(200):
+                self.flush.fill_(1)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); self.launch(i); b.record()
+                ts.append((a, b))
+            torch.cuda.synchronize()
+            us = sorted(a.elapsed_time(b) * 1e3 for a, b in ts)
+            med, p99 = us[len(us) // 2], us[int(len(us) * 0.99) - 1]
+            out.append({"kernel": c[0], "us": round(med, 2), "us_p99": round(p99, 2), "TFLOP/s": round(self.FLOPS / (med * 1e-6) / 1e12, 3)})
+        return out
+
+    def cpu_run(self, orc, n, threads, reps=1):
+        import numpy as np
+        rng = np.random.default_rng(0xB201)
+        q, k, v = (rng.uniform(-1, 1, (self.B, self.H, self.S, self.D)).astype(np.float32) for _ in range(3))
+        t0 = time.perf_counter()
+        for _ in range(reps * n):
+            orc.cpu_prefill(q, k, v, self.D, self.S, self.S, self.H, self.H, self.B, 0, threads=threads)
+        dt = (time.perf_counter() - t0) / (reps * n)
+        return self.FLOPS / dt / 1e12, dt
+
+    cpu_sample = 8
+    cpu_sample_text = "the full shape (8 heads over the host threads), 8 passes"
+
+
+# --------------------------------------------------------------------------------------
+# workload: the device-level wave API in the reference's own terms (secondary, labelled)
+# --------------------------------------------------------------------------------------
+class WaveApi:
+    name = "wave_api"
+    metric = "LayerNorm + softmax rows on the wave primitives (one warp per row; algorithmic bytes), with the register-resident reduce loop as context"
+    unit = "GB/s"
+    dtype = "f32 (loop: f32, f64, i32)"
+    BYTES = 65536 * 512 * 4                                          # one operand; rows x cols = 2^25 floats at either width
+
+    def __init__(self, n=None):
+        self.cases = [(f"{which}<{cols} cols, {backend}>", which, cols, backend, 2 * self.BYTES)
+                      for which in ("layernorm", "softmax") for cols in (64, 512) for backend in ("primitives", "portable")]
+        self.bytes_per_step = sum(c[4] for c in self.cases)
+
+    def config(self, world):
+        return {"workload": "device-level wave API: LayerNorm / softmax rows (bench_layernorm.hip, bench_softmax.hip of the reference) "
+                            "and its register-resident reduce loop (bench_reduce_dpp_types.hip)",
+                "rows": {"64": self.BYTES // 256, "512": self.BYTES // 2048}, "launches_per_step": len(self.cases),
+                "sharding": f"replicas x{world}, no collective",
+                "l2": "a 256 MB buffer is written between timed launches of the per-kernel timing; in/out are 134 MB each",
+                "loop": "4736 waves x 64 values x 4096 repetitions per launch, no memory traffic inside the loop; Gelem/s",
+                "context": "the reference quotes its primitives in these terms (elements per second of the reduce loop on MI300X); "
+                           "an HBM roofline does not apply to the loop",
+                "inputs": "N(0,1)*3, seeded"}
+
+    def setup(self, torch, pkg, device, rank):
+        self.torch, self.pkg = torch, pkg
+        g = torch.Generator(device=device); g.manual_seed(0xB206)
+        n = self.BYTES // 4
+        self.x = {64: torch.randn(n // 64, 64, device=device, generator=g) * 3, 512: torch.randn(n // 512, 512, device=device, generator=g) * 3}
+        self.gb = {c: (torch.randn(c, device=device, generator=g), torch.randn(c, device=device, generator=g)) for c in (64, 512)}
+        self.out = {c: torch.empty_like(self.x[c]) for c in (64, 512)}
+        self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=device)
+        self.xh = self.x[512].cpu().pin_memory()
+        self.oh = torch.empty(self.x[512].shape, dtype=torch.float32).pin_memory()
+        torch.cuda.synchronize()
+
+    def launch(self, i):
+        _l, which, cols, backend, _b = self.cases[i]
+        g, b = self.gb[cols]
+        self.pkg.row_op(which, self.x[cols], g, b, backend, out=self.out[cols])
+
+    def step(self, events=None):
+        for i in range(len(self.cases)):
+            self.launch(i)
+
+    def step_e2e(self):
+        self.x[512].copy_(self.xh, non_blocking=True)
+        self.launch(2)                                              # layernorm, 512 columns, primitives
+        self.oh.copy_(self.out[512], non_blocking=True)
+
+    e2e_units = 2 * BYTES
+
+    def e2e_bytes(self):
+        return self.BYTES, self.BYTES
+
+    def per_kernel(self):
+        torch = self.torch
+        res = []
+        for i, c in enumerate(self.cases):
+            for _ in range(5):
+                self.launch(i)
+            ts = []
+            for _ in range(30):
+                self.flush.fill_(1)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); self.launch(i); b.record()
+                ts.append((a, b))
+            torch.cuda.synchronize()
+            us = sorted(a.elapsed_time(b) * 1e3 for a, b in ts)[len(ts) // 2]
+            res.append({"kernel": c[0], "us": round(us, 2), "bytes": c[4], "GB/s": round(c[4] / (us * 1e-6) / 1e9, 1)})
+        return res
+
+    def extra_fields(self):
+        """The reduce loop, primitives against the portable shuffle loop: Gelem/s (median of 20 launches)."""
+        torch, pkg = self.torch, self.pkg
+        waves, reps = 4736, 4096
+        out = {}
+        for dt, name in ((torch.float32, "f32"), (torch.int32, "i32"), (torch.float64, "f64")):
+            x = (torch.arange(64 * waves, device=self.x[64].device) % 64).to(dt)
+            o = torch.empty(waves, dtype=dt, device=x.device)
+            for op in ("sum", "max"):
+                for backend in ("primitives", "portable"):
+                    for _ in range(3):
+                        pkg.wave_reduce_loop(x, op, reps, backend, out=o)
+                    ts = []
+                    for _ in range(20):
+                        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        a.record(); pkg.wave_reduce_loop(x, op, reps, backend, out=o); b.record()
+                        ts.append((a, b))
+                    torch.cuda.synchronize()
+                    ms = sorted(a.elapsed_time(b) for a, b in ts)[10]
+                    out[f"reduce_{op}<{name}> {backend}"] = round(64.0 * waves * reps / (ms * 1e-3) / 1e9, 1)
+        return {"wave_reduce_loop_Gelem_per_s": out}
+
+    def cpu_run(self, orc, n, threads, reps=1):
+        """n = thousands of rows of 512 columns: numpy LayerNorm + softmax (the CPU statement of the two row kernels)."""
+        import numpy as np
+        x = (np.random.default_rng(6).standard_normal((n * 1024, 512)) * 3).astype(np.float32)
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            m = x.mean(axis=1, keepdims=True); v = ((x - m) ** 2).mean(axis=1, keepdims=True)
+            _ = (x - m) / np.sqrt(v + 1e-5)
+            e = np.exp(x - x.max(axis=1, keepdims=True)); _ = e / e.sum(axis=1, keepdims=True)
+        dt = (time.perf_counter() - t0) / reps
+        return 2 * 2 * x.nbytes / dt / 1e9, dt
+
+    cpu_sample = 16
+    cpu_sample_text = "16384 rows of 512 columns, LayerNorm + softmax in numpy (one thread)"
+
+
+WORKLOADS = {"wave_api": WaveApi, "fa_steps": FaSteps, "segops": SegopsSweep, "decode": DecodeGQA, "prefill": PrefillCausal, "decode_long": DecodeLong,
              "runtime": RuntimeLlama}
-ALL_ORDER = ["segops", "decode", "prefill"]          # `--workload all`: the first is the headline
+ALL_ORDER = ["prefill", "decode", "segops", "decode_long", "runtime", "fa_steps", "wave_api"]   # `--workload all`: the first is the headline
 
 
 def make_workload(name, elements=None):
@@ -557,6 +835,38 @@ def make_workload(name, elements=None):
 
 
 # --------------------------------------------------------------------------------------
+def load_traffic():
+    """Measured DRAM traffic per launch of the dominant kernels: a small tracked data file kept beside the
+    profiler summaries it was read from (each entry names its summary and how it scales)."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except OSError:
+        return {}
+
+
+def traffic_for(label, units_bytes, table):
+    """Bytes of DRAM traffic per launch for a kernel label, or None when no capture covers it."""
+    try:
+        if label.startswith("reduce_") and "f16" not in label and "bf16" not in label:
+            t = table["segreduce"]
+            n_in = units_bytes * 64 / 65                          # units = n*size + n/64*size
+            return int(n_in * t["read_factor"] + (units_bytes - n_in) * t["result_factor"])
+        if label.startswith("scan_inclusive_sum<f16") or label.startswith("scan_inclusive_sum<bf16"):
+            return int(table["segscan_16bit"]["bytes_at_2p26"] * units_bytes / (2 * (1 << 26) * 2))
+        if label.startswith("scan_"):
+            t = table["segscan"]
+            return int(units_bytes / 2 * (t["read_factor"] + t["write_factor"]))
+        if label.startswith("decode_mma_kernel"):
+            return int(table["decode_mma_kernel"]["bytes"]) if units_bytes == 2148532224 else None
+        if label.startswith("prefill_tc_kernel"):
+            return int(table["prefill_tc_kernel"]["bytes"])
+    except (KeyError, TypeError):
+        pass
+    return None
+
+
 def cpu_line(wl, orc, steps, budget_s=120.0):
     """The CPU statement of the workload (oracle) on the host cores: median over `steps`
     runs of a bounded sample."""
@@ -580,7 +890,7 @@ def reference_arm(args, names, rank, world, emit):
     lines = []
     for name in names:
         wl = make_workload(name, args.elements)
-        v, dt, n, threads = cpu_line(wl, orc, args.steps, budget_s=120.0 / len(names))
+        v, dt, n, threads = cpu_line(wl, orc, min(args.steps, 5), budget_s=100.0 / len(names))
         lines.append({"impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus,
                       "steps": n, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
                       "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": wl.dtype,
@@ -599,7 +909,7 @@ def measure(wl, args, ctx):
     Returns the JSON-ready dict (on every rank; rank 0 prints)."""
     torch, dist, pkg = ctx["torch"], ctx["dist"], ctx["pkg"]
     device, rank, world, local_rank = ctx["device"], ctx["rank"], ctx["world"], ctx["local_rank"]
-    peaks = ctx["peaks"]
+    peaks, traffic = ctx["peaks"], ctx["traffic"]
 
     def barrier():
         if world > 1:
@@ -613,7 +923,8 @@ def measure(wl, args, ctx):
         return float(t.item())
 
     wl.setup(torch, pkg, device, rank)
-    warm = max(args.warmup, 3)
+    steps = args.steps if wl.name != "runtime" else max(2, min(args.steps, 5))     # a runtime step is a whole generation
+    warm = max(args.warmup, 3) if wl.name != "runtime" else 3
     for _ in range(warm):
         wl.step()
     barrier()
@@ -624,42 +935,31 @@ def measure(wl, args, ctx):
         barrier()
         t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         t0.record()
-        for _ in range(args.steps):
+        for _ in range(steps):
             wl.step()
         t1.record()
         barrier()
     launches = pkg.launch_count() - launches0
-    ms_per_step = max_over_ranks(t0.elapsed_time(t1)) / args.steps
+    ms_per_step = max_over_ranks(t0.elapsed_time(t1)) / steps
     tensor_bound = getattr(wl, "bound", "hbm") == "tensor"
     unit_scale = 1e12 if tensor_bound else (1.0 if wl.unit == "tokens/s" else 1e9)
     peak = peaks["bf16_tflops"] if tensor_bound else peaks["hbm_gbs"]
     value = world * wl.bytes_per_step / (ms_per_step * 1e-3) / unit_scale
 
     # ---- per-kernel durations ------------------------------------------------------------
-    # (a) inside the step: the same steps again with one event after every launch (each event
-    #     costs ~3 us of stream time, and a launch is charged for write-backs its predecessor left
-    #     in L2); (b) where the workload has several kernels, each one alone: `reps` launches back
-    #     to back between two events, alternating between two input buffers so that no launch finds
-    #     its input in L2 -- the kernel's own average launch duration.
+    # One kernel per step: its average launch duration over the timed region itself.  Several kernels per
+    # step (the sweep): each one alone, 20 launches back to back between two events, alternating between two
+    # input buffers so that no launch finds its input in L2 -- the kernel's own average launch duration.
     ncase = len(wl.cases)
-    if ncase == 1:
-        # one kernel per step: its average launch duration over the timed region itself
-        isteps, per = 1, [ms_per_step]
-    else:
-        isteps = max(1, min(args.steps, 10))
-        events = [torch.cuda.Event(enable_timing=True)]
-        events[0].record()
-        for _ in range(isteps):
-            wl.step(events)
-        barrier()
-        per = [0.0] * ncase
-        for s_ in range(isteps):
-            for i in range(ncase):
-                per[i] += events[s_ * ncase + i].elapsed_time(events[s_ * ncase + i + 1])
-    alone = None
-    if hasattr(wl, "launch_case"):
-        reps, alone = 20, []
-        for i in range(ncase):
+    kernels = []
+    strong = getattr(wl, "scaling", "weak") == "strong"
+    if hasattr(wl, "per_kernel"):
+        kernels = wl.per_kernel()
+        for k in kernels:
+            k["frac"] = round(k[wl.unit] / peak, 5)
+    elif hasattr(wl, "launch_case"):
+        reps = 20
+        for i, (label, fn, kind, op, units) in enumerate(wl.cases):
             for r in range(4):
                 wl.launch_case(i, r)
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -668,28 +968,35 @@ def measure(wl, args, ctx):
                 wl.launch_case(i, r)
             b.record()
             b.synchronize()
-            alone.append(a.elapsed_time(b) / reps)
-    kernels = []
-    for i, (label, fn, kind, op, units) in enumerate(wl.cases):
-        units = units / world if getattr(wl, "scaling", "weak") == "strong" else units
-        us_step = max(per[i] / isteps * 1e3, 1e-3)
-        us = max(alone[i] * 1e3, 1e-3) if alone is not None else us_step
+            us = max(a.elapsed_time(b) / reps * 1e3, 1e-3)
+            rate = units / (us * 1e-6) / unit_scale
+            kernels.append({"kernel": label, "us": round(us, 2), "bytes": units, wl.unit: round(rate, 1), "frac": round(rate / peak, 4)})
+    else:
+        label, _f, _k, _o, units = wl.cases[0]
+        units = units / world if strong else units
+        us = ms_per_step * 1e3
         rate = units / (us * 1e-6) / unit_scale
-        k = {"kernel": label, "us": round(us, 2), "flops" if tensor_bound else "bytes": units,
-             wl.unit: round(rate, 1), "frac": round(rate / peak, 4)}
-        if alone is not None:
-            k["us_inside_step"] = round(us_step, 2)
-        kernels.append(k)
-    dom = max(range(ncase), key=lambda i: per[i])
-    roofline = {"bound": "tensor" if tensor_bound else "hbm", "kernel": kernels[dom]["kernel"],
-                "achieved": kernels[dom][wl.unit], "peak": peak, "unit": wl.unit, "frac": kernels[dom]["frac"],
+        kernels.append({"kernel": label, "us": round(us, 2), "flops" if tensor_bound else "bytes": units,
+                        wl.unit: round(rate, 1), "frac": round(rate / peak, 4)})
+    # the roofline names the kernel FURTHEST below its roof
+    low = min(kernels, key=lambda k: k["frac"])
+    roofline = {"bound": "tensor" if tensor_bound else "hbm", "kernel": low["kernel"],
+                "achieved": low[wl.unit], "peak": peak, "unit": wl.unit, "frac": low["frac"],
                 "peak_source": f"{peaks['source']} " + ("cuBLAS bf16 burst" if tensor_bound else "copy bandwidth"),
-                "timing": ("CUDA events around 20 back-to-back launches of this kernel on alternating input buffers"
-                           if alone is not None else "CUDA events around the timed region / launches in it"),
-                "traffic": TRAFFIC.get(kernels[dom]["kernel"])}
+                "timing": ("CUDA events around back-to-back launches of this kernel alone (inputs alternate between buffers larger than L2)"
+                           if hasattr(wl, "launch_case") else
+                           "one CUDA event pair per launch, L2 flushed before each" if hasattr(wl, "per_kernel") else
+                           "CUDA events around the timed region / launches in it"),
+                "lowest_of": len(kernels),
+                "traffic": traffic_for(low["kernel"], low.get("bytes", low.get("flops", 0)), traffic)}
+    if len(kernels) > 8:                                           # keep the record short: the extremes, not all twenty
+        ks = sorted(kernels, key=lambda k: k["frac"])
+        kernels = ks[:4] + ks[-2:]
 
     # ---- end to end: host buffers in, host results out, every step ----------------------
-    e2e_steps = args.e2e_steps or max(3, min(args.steps, 10))
+    e2e_steps = args.e2e_steps or max(3, min(steps, 10))
+    if hasattr(wl, "setup_e2e"):
+        wl.setup_e2e()
     wl.step_e2e()
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -700,43 +1007,69 @@ def measure(wl, args, ctx):
     barrier()
     e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / e2e_steps
     h2d, d2h = wl.e2e_bytes()
-    e2e = {"value": world * wl.bytes_per_step / (e2e_ms * 1e-3) / unit_scale, "unit": wl.unit, "ms_per_step": e2e_ms,
+    e2e_units = getattr(wl, "e2e_units", wl.bytes_per_step)
+    e2e = {"value": world * e2e_units / (e2e_ms * 1e-3) / unit_scale, "unit": wl.unit, "ms_per_step": e2e_ms,
            "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps}
+    if hasattr(wl, "e2e_note"):
+        e2e["how"] = wl.e2e_note
+    if hasattr(wl, "setup_e2e"):
+        # the same bytes moved with no kernel launched: what the copies alone cost on this box at this N
+        wl.step_e2e(compute=False)
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record()
+        for _ in range(e2e_steps):
+            wl.step_e2e(compute=False)
+        f1.record()
+        barrier()
+        e2e["e2e_floor_ms"] = max_over_ranks(f0.elapsed_time(f1)) / e2e_steps
 
     # ---- CPU baseline (rank 0, N = 1 only) ----------------------------------------------
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         import oracle as orc
-        v, dt, n, threads = cpu_line(wl, orc, 3, budget_s=30.0)
+        v, dt, n, threads = cpu_line(wl, orc, 3, budget_s=12.0)
         cpu = {"value": v, "unit": wl.unit, "cores": threads, "kind": "port",
                "sample": f"{wl.cpu_sample_text}, median of {n} runs of {dt:.2f} s; independent units split over {threads} host threads"}
 
-    if hasattr(wl, "extra"):
-        ex = wl.extra()
-        roofline = {"bound": "hbm", "kernel": "decode step (weights + KV cache streamed once per token)",
-                    "achieved": round(ex["decode_hbm_GBs"], 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                    "frac": round(ex["decode_hbm_GBs"] / peaks["hbm_gbs"], 4),
-                    "peak_source": f"{peaks['source']} copy bandwidth", "traffic": None}
-        kernels = [ex]
-    return {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+    line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": steps,
             "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
             "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": wl.dtype,
-            "data": "synthetic (seeded)", "config": wl.config(world), "clocks": clk.summary(), "e2e": e2e,
+            "data": "synthetic (seeded)", "config": None, "clocks": clk.summary(), "e2e": e2e,
             "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu, "kernels": kernels}
+    if hasattr(wl, "extra"):
+        ex = wl.extra()
+        line["roofline"] = {"bound": "hbm", "kernel": "decode step (weights + KV cache streamed once per token)",
+                            "achieved": round(ex["decode_hbm_GBs"], 1), "peak": peaks["hbm_gbs"], "unit": "GB/s",
+                            "frac": round(ex["decode_hbm_GBs"] / peaks["hbm_gbs"], 4),
+                            "peak_source": f"{peaks['source']} copy bandwidth", "traffic": None}
+        line["kernels"] = [ex]
+    if hasattr(wl, "extra_fields"):
+        line.update(wl.extra_fields())
+    if hasattr(wl, "time_other_exchange"):
+        other = wl.time_other_exchange(steps, barrier, max_over_ranks)
+        if other is not None:
+            line["other_exchange"] = other
+        par = wl.parity()
+        if par is not None or world > 1:
+            line["parity_max_abs"] = par
+            line["parity_how"] = "rank 0, sequences 0 and 63: sharded result vs one decode launch over the gathered KV sequence (bf16 outputs)"
+    line["config"] = wl.config(world)
+    return line
 
 
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--workload", default="all", choices=sorted(WORKLOADS) + ["all"],
-                    help="all = segops (headline) with decode and prefill reported under 'others'")
+                    help="all = prefill (headline) with the other five reported under 'others'")
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer (end-to-end) measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--exchange", default="auto", choices=["auto", "peer", "nccl"],
-                    help="decode_long at N>1: how the (O, lse) partials cross the GPUs")
+                    help="decode_long at N>1: how the (O, lse) partials cross the GPUs in the timed region")
     ap.add_argument("--elements", type=int, default=None,
                     help="problem size override (elements per dtype / kv length / seq length); "
                          "smaller cases are for profiler captures only")
@@ -771,7 +1104,7 @@ def main():
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     ctx = {"torch": torch, "dist": dist, "pkg": pkg, "device": device, "rank": rank, "world": world,
-           "local_rank": local_rank, "peaks": load_peaks()}
+           "local_rank": local_rank, "peaks": load_peaks(), "traffic": load_traffic()}
     lines = []
     for name in names:
         wl = make_workload(name, args.elements)
@@ -781,6 +1114,8 @@ def main():
         if hasattr(wl, "dec"):
             wl.dec.check()                      # a bounded wait of the peer exchange that ran out is an error
         del wl
+        import gc
+        gc.collect()
         torch.cuda.empty_cache()
     if rank == 0:
         line = lines[0]
@@ -790,26 +1125,6 @@ def main():
     if world > 1:
         dist.destroy_process_group()
 
-
-# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures
-# summarised under profiles/, scaled from the captured case to a full launch by the units
-# processed (traffic of these streaming kernels is proportional to them).
-def _seg_traffic():
-    t = {}
-    for kind, size in (("f32", 4), ("i32", 4), ("f64", 8), ("i64", 8)):
-        for op in ("sum", "max", "min"):                      # profiles/segreduce_f32_sum_2p25.md: read 1.00x, results 3x
-            t[f"reduce_{op}<{kind}>"] = (1 << 26) * size + 3 * (1 << 20) * size
-        # profiles/segscan_f64_sum_2p25.md: read 1.00x; 78 % of the output reached DRAM before the launch ended
-        t[f"scan_inclusive_sum<{kind}>"] = int((1 << 26) * size * (1.0 + 0.784))
-    for kind in ("f16", "bf16"):                                  # profiles/segscan_lane_16bit_sum_2p26.md: 215 MB of 268 MB
-        t[f"scan_inclusive_sum<{kind}>"] = 215_000_000
-    return t
-
-
-TRAFFIC = _seg_traffic()
-# profiles/decode_mma_bf16_d128_n8192_full.md and profiles/prefill_tc_bf16_d128_s4096_full.md: full-size captures
-TRAFFIC["decode_mma_kernel (+ combine)"] = int(7.130e12 * 301.984e-6)
-TRAFFIC["prefill_tc_kernel"] = int(793.7e9 * 1.332064e-3)
 
 if __name__ == "__main__":
     main()

@@ -108,6 +108,22 @@ int b200p_wave_probe_n(int fn, int op, int dtype, const void* in, void* out, int
  * first elements, [7] lane_mask_lt() of lane 5. */
 int b200p_wave_vote_probe(const int* in64, unsigned long long* out8, b200p_stream_t stream);
 
+/* The register-resident reduce loop with which the reference measures its device-level primitives
+ * (research/wave-primitives/benchmarks/bench_reduce_dpp_types.hip:29-45): each of n_waves waves (a multiple of 8;
+ * in: 64 * n_waves values, out: n_waves values) reduces its 64 values `reps` times with the result fed back into
+ * the inputs, no memory traffic inside the loop.  backend 0: wave::dpp::reduce_* of wave64.cuh (pair per lane);
+ * backend 1: the portable shuffle-down loop + broadcast the reference compares against.  f32 / f64 / i32 / i64.
+ * The caller times the launch; throughput = 64 * n_waves * reps elements per launch. */
+int b200p_wave_reduce_loop(int op, int dtype, int backend, const void* in, void* out, int n_waves, int reps,
+                           b200p_stream_t stream);
+
+/* The reference's two "real kernel" benchmarks of the primitives, one wave per row
+ * (research/wave-primitives/benchmarks/bench_layernorm.hip:47-96, bench_softmax.hip):
+ * which 0: out = LayerNorm(x) * gamma + beta (two row sums);  which 1: out = softmax(x) (row max + row sum).
+ * x, out [rows, cols] fp32 with cols 64 or 512; gamma, beta [cols] (LayerNorm only); backend as above. */
+int b200p_row_op(int which, int backend, int cols, const float* x, const float* gamma, const float* beta, float* out,
+                 int rows, float eps, b200p_stream_t stream);
+
 /* Kernels that use the facade headers the way a caller of the reference would
  * (cdna3-prims/tests/compile_smoke.hip:24-50; include <cdna3/cdna3.hpp> and
  * <cdna3/examples/fused_softmax.hpp>):

@@ -113,9 +113,23 @@ int b200p_skinny_gemm(int dtype, int prologue, int epilogue, const void* W, cons
                       const void* norm_w, void* out, int M, int N, int K, int ldx, int ldo, float eps,
                       b200p_stream_t stream);
 
+/* C[M, N] = A[M, K] . W[N, K]^T on the tensor cores (tcgen05, fp32 accumulation in tensor memory), the
+ * prefill-side counterpart of b200p_skinny_gemm: stands in for RocblasHandle::gemm_* at their call sites in
+ * Session::run_layers (rocblas_gemm.hpp:112-209; session.hpp:147-160,171-173,220,227-230) with the element-wise
+ * kernel that follows each GEMM in the reference folded into the epilogue:
+ *   epilogue 0: C 16-bit;  2: C fp32;  1: C fp32 += product (the residual add, forward.hpp add_f32_kernel);
+ *   epilogue 3: W is [2N, K] (gate rows, then up rows), C 16-bit = SiLU(gate) * up (forward.hpp:154-160).
+ * A [M, lda] and W [N, ldw] 16-bit, row-major; lda, ldw, K multiples of 8; A, W 16-byte and C 32-byte aligned
+ * with rows of C on 32 bytes.  B200P_E_RANGE / B200P_E_ALIGN for anything else (nothing is launched). */
+int b200p_gemm_16(int dtype, int epilogue, const void* A, const void* W, void* C, int M, int N, int K,
+                  long long lda, long long ldw, long long ldc, b200p_stream_t stream);
+
 int b200p_session_kv_len(const b200p_session* s);
-/* Kernels of this library + cuBLAS GEMM calls issued by the session so far. */
+/* Projections (matrix products) issued by the session so far, and how many of them went to the GEMM
+ * library (cuBLAS) rather than to this library's own kernels: 0 unless a shape or pointer is outside
+ * those kernels' domain or b200p_set_tuning("runtime_gemm" / "runtime_skinny", 0). */
 unsigned long long b200p_session_gemm_calls(const b200p_session* s);
+unsigned long long b200p_session_blas_calls(const b200p_session* s);
 /* Decode steps of b200p_session_generate that ran as replays of the captured step graph
  * (every step after the first of a call, unless b200p_set_tuning("runtime_graph", 0)). */
 unsigned long long b200p_session_graph_replays(const b200p_session* s);

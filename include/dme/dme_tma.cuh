@@ -99,8 +99,12 @@ __device__ __forceinline__ void copy_tile_1d_stream(void* smem_dst, const void* 
                  :: "r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy) : "memory");
 }
 
-// Tiled 4-D tensor-map copy: box at element coordinates (x, y, z, w); x * element size
+// Tiled tensor-map copies: box at element coordinates (x, y[, z, w]); x * element size
 // must be a multiple of 16 bytes.
+__device__ __forceinline__ void copy_tile_2d(void* smem_dst, const void* tensor_map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(smem_addr(smem_dst)), "l"(tensor_map), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void copy_tile_4d(void* smem_dst, const void* tensor_map, int x, int y, int z, int w, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
                  :: "r"(smem_addr(smem_dst)), "l"(tensor_map), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");

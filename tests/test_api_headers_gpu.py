@@ -46,3 +46,37 @@ def test_async_tile_ping_pong_and_tile_1d(b200p, torch_cuda):
     f = torch.randn(11, 256, device="cuda")
     got = b200p.api_probe(4, f, 1, 11).view(11, 256)
     assert torch.equal(got, f + 1)
+
+
+@pytest.mark.parametrize("backend", ["primitives", "portable"])
+@pytest.mark.parametrize("dt", ["float32", "float64", "int32", "int64"])
+def test_register_resident_reduce_loop(b200p, torch_cuda, dt, backend):
+    """The reference's microbenchmark loop (bench_reduce_dpp_types.hip:29-45) computes what a host loop computes:
+    integer-valued data keeps every type exact."""
+    torch = torch_cuda
+    dtype = getattr(torch, dt)
+    waves, reps = 64, 5
+    x = (torch.arange(64 * waves, device="cuda") % 7).to(dtype)
+    lane = torch.arange(64, device="cuda").to(dtype) + 1
+    for op, fn in (("sum", lambda t: t.sum(dim=1)), ("max", lambda t: t.max(dim=1).values), ("min", lambda t: t.min(dim=1).values)):
+        got = b200p.wave_reduce_loop(x, op, reps, backend)
+        v, acc = x.view(waves, 64).clone(), torch.zeros(waves, device="cuda", dtype=dtype)
+        for _ in range(reps):
+            s = fn(v)
+            acc = acc + s
+            v = s[:, None] + lane[None, :]
+        assert torch.equal(got, acc), (dt, op)
+
+
+@pytest.mark.parametrize("backend", ["primitives", "portable"])
+@pytest.mark.parametrize("cols", [64, 512])
+def test_layernorm_and_softmax_rows(b200p, torch_cuda, cols, backend):
+    torch = torch_cuda
+    g = torch.Generator(device="cuda"); g.manual_seed(cols)
+    x = torch.randn(4099, cols, device="cuda", generator=g) * 3
+    gamma, beta = torch.randn(cols, device="cuda", generator=g), torch.randn(cols, device="cuda", generator=g)
+    ln = b200p.row_op("layernorm", x, gamma, beta, backend)
+    ref = torch.nn.functional.layer_norm(x.double(), (cols,), gamma.double(), beta.double(), 1e-5)
+    assert (ln.double() - ref).abs().max().item() < 2e-5
+    sm = b200p.row_op("softmax", x, backend=backend)
+    assert (sm.double() - torch.softmax(x.double(), dim=1)).abs().max().item() < 1e-6
