@@ -18,7 +18,12 @@
 // TMA loads [rows][64 x 16-bit] boxes with the 128-byte swizzle into a ring of
 // shared-memory stages, ONE thread issues tcgen05.mma (M = 128, N = BN, K = 16) with the
 // fp32 accumulator in tensor memory, and a warpgroup reads the finished accumulator
-// back (one row per thread) for the epilogue.  CTAs are persistent (one per SM) and
+// back (one row per thread), applies the epilogue and hands the result to the TMA
+// engine 128 bytes of columns at a time: rows go to a swizzled shared-memory staging
+// tile (two buffers), and one thread issues a tensor-map store -- or, for the residual
+// form, a tensor-map fp32 add-reduction into C, so the read-modify-write happens in L2
+// without a register round trip.  Rows past M and columns past N are clipped by the
+// tensor map, so there is no tail code.  CTAs are persistent (one per SM) and
 // walk the tiles m-fastest, so the CTAs in flight at any time share a few W tiles in
 // L2; two accumulator buffers (2 x 256 columns = all of tensor memory) let the
 // epilogue of tile i run under the MMAs of tile i+1.
@@ -47,7 +52,9 @@ template <int BN> struct GemmShape {
     static constexpr int B_BYTES = BN * kTK * 2;             // 16 / 32 KB
     static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
     static constexpr int STAGES = BN == 256 ? 4 : 6;
-    static constexpr int OFF_BAR = STAGES * STAGE_BYTES;
+    static constexpr int OFF_OUT = STAGES * STAGE_BYTES;     // two staging tiles [128 rows][128 B] for the epilogue
+    static constexpr int OUT_BYTES = kTM * 128;
+    static constexpr int OFF_BAR = OFF_OUT + 2 * OUT_BYTES;
     static constexpr int SMEM_BYTES = OFF_BAR + 256;
 };
 
@@ -63,19 +70,11 @@ template <typename T> struct GFmt;
 template <> struct GFmt<__half>        { static constexpr int id = 0; };
 template <> struct GFmt<__nv_bfloat16> { static constexpr int id = 1; };
 
-__device__ __forceinline__ void st_v8(void* p, const uint32_t (&w)[8]) {
-    asm volatile("st.global.v8.b32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};"
-                 :: "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]), "r"(w[4]), "r"(w[5]), "r"(w[6]), "r"(w[7]), "l"(p) : "memory");
-}
-__device__ __forceinline__ void ld_v8(const void* p, uint32_t (&w)[8]) {
-    asm volatile("ld.global.v8.b32 {%0,%1,%2,%3,%4,%5,%6,%7}, [%8];"
-                 : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]) : "l"(p) : "memory");
-}
-
 // BN: accumulator columns per tile (for EPI_SILU16: BN/2 gate columns and the BN/2 matching up columns).
 template <typename T, int BN, int EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW) {
+gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapW,
+               const __grid_constant__ CUtensorMap mapC) {
     using Sh = GemmShape<BN>;
     constexpr int ST = Sh::STAGES;
     constexpr int OUT_N = EPI == GEMM_EPI_SILU16 ? BN / 2 : BN;     // output columns per tile
@@ -158,73 +157,66 @@ gemm_tc_kernel(const GemmParams p, const __grid_constant__ CUtensorMap mapA, con
         }
     } else {
         // ---------------------------------- epilogue warps --------------------------------
+        constexpr bool OUT16 = EPI == GEMM_EPI_STORE16 || EPI == GEMM_EPI_SILU16;
+        constexpr int GCOLS = OUT16 ? 64 : 32;                // output columns per 128-byte group
         const int q = warp & 3;                               // TMEM lane quarter this warp may touch
         const int r = q * 32 + lane;                          // row inside the tile
         const uint32_t lane_base = uint32_t(32 * q) << 16;
-        int it = 0;
+        const bool issuer = threadIdx.x == 64;                // first epilogue thread: issues and tracks the stores
+        if (issuer) dme::prefetch_tensor_map(&mapC);
+        int it = 0, grp = 0;
         for (int tile = blockIdx.x; tile < ntiles && ok; tile += gridDim.x, ++it) {
             const int b = it & 1;
             const int tm = tile % p.tiles_m, tn = tile / p.tiles_m;
-            if (!dme::wait(&acc_full[b], uint32_t((it >> 1) & 1), p.abort_word)) { ok = false; break; }
+            // The 128 epilogue threads meet at named barriers below, so they must leave this loop TOGETHER: the outcome
+            // of the wait is and-reduced over all of them (a barrier every one of them reaches) before anyone acts on it.
+            const bool got = dme::wait(&acc_full[b], uint32_t((it >> 1) & 1), p.abort_word);
+            uint32_t all_got;
+            asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, 3, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(all_got) : "r"(uint32_t(got)) : "memory");
+            if (!all_got) { ok = false; break; }
             tc::fence_after_sync();
-            const int row = tm * kTM + r;
-            const int col0 = tn * OUT_N;
             const uint32_t tacc = tmem + lane_base + uint32_t(b * 256);
             #pragma unroll 1
-            for (int c = 0; c < OUT_N / 32; ++c) {
-                uint32_t v[32];
-                tc::ld_32x32b_x32(tacc + c * 32, v);
-                uint32_t u[32];
-                if (EPI == GEMM_EPI_SILU16) tc::ld_32x32b_x32(tacc + OUT_N + c * 32, u);
-                tc::wait_ld();
-                const int col = col0 + c * 32;
-                if (row < p.M && col < p.N) {
-                    const bool whole = col + 32 <= p.N;
-                    if (EPI == GEMM_EPI_STORE16 || EPI == GEMM_EPI_SILU16) {
-                        T* dst = static_cast<T*>(p.C) + size_t(row) * p.ldc + col;
-                        uint32_t w[16];
-                        #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            float x0 = __uint_as_float(v[2 * i]), x1 = __uint_as_float(v[2 * i + 1]);
-                            if (EPI == GEMM_EPI_SILU16) {
-                                x0 = (x0 / (1.f + __expf(-x0))) * __uint_as_float(u[2 * i]);
-                                x1 = (x1 / (1.f + __expf(-x1))) * __uint_as_float(u[2 * i + 1]);
-                            }
-                            w[i] = pack2<T>(x0, x1);
-                        }
-                        if (whole) {
-                            st_v8(dst, *reinterpret_cast<uint32_t(*)[8]>(&w[0]));
-                            st_v8(dst + 16, *reinterpret_cast<uint32_t(*)[8]>(&w[8]));
-                        } else {
-                            const T* h = reinterpret_cast<const T*>(w);
-                            for (int i = 0; col + i < p.N; ++i) dst[i] = h[i];
-                        }
-                    } else {
-                        float* dst = static_cast<float*>(p.C) + size_t(row) * p.ldc + col;
-                        if (whole) {
-                            #pragma unroll
-                            for (int g = 0; g < 4; ++g) {
-                                uint32_t w[8];
-                                if (EPI == GEMM_EPI_ACC32) {
-                                    ld_v8(dst + g * 8, w);
-                                    #pragma unroll
-                                    for (int i = 0; i < 8; ++i) w[i] = __float_as_uint(__uint_as_float(w[i]) + __uint_as_float(v[g * 8 + i]));
-                                } else {
-                                    #pragma unroll
-                                    for (int i = 0; i < 8; ++i) w[i] = v[g * 8 + i];
-                                }
-                                st_v8(dst + g * 8, w);
-                            }
-                        } else {
-                            for (int i = 0; col + i < p.N; ++i)
-                                dst[i] = EPI == GEMM_EPI_ACC32 ? dst[i] + __uint_as_float(v[i]) : __uint_as_float(v[i]);
-                        }
+            for (int c = 0; c < OUT_N / GCOLS; ++c, ++grp) {
+                uint32_t v[GCOLS], w[32];                      // accumulator columns of this group; 128 bytes of output
+                #pragma unroll
+                for (int h = 0; h < GCOLS / 32; ++h) tc::ld_32x32b_x32(tacc + c * GCOLS + h * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[h * 32]));
+                if (EPI == GEMM_EPI_SILU16) {
+                    uint32_t u[GCOLS];
+                    #pragma unroll
+                    for (int h = 0; h < GCOLS / 32; ++h) tc::ld_32x32b_x32(tacc + OUT_N + c * GCOLS + h * 32, *reinterpret_cast<uint32_t(*)[32]>(&u[h * 32]));
+                    tc::wait_ld();
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) {              // SiLU on the SFU: one ex2 and one approximate divide per element
+                        const float g0 = __uint_as_float(v[2 * i]), g1 = __uint_as_float(v[2 * i + 1]);
+                        w[i] = pack2<T>(__fdividef(g0, 1.f + __expf(-g0)) * __uint_as_float(u[2 * i]),
+                                        __fdividef(g1, 1.f + __expf(-g1)) * __uint_as_float(u[2 * i + 1]));
                     }
+                } else {
+                    tc::wait_ld();
+                    #pragma unroll
+                    for (int i = 0; i < 32; ++i) w[i] = OUT16 ? pack2<T>(__uint_as_float(v[(2 * i) % GCOLS]), __uint_as_float(v[(2 * i + 1) % GCOLS])) : v[i % GCOLS];
+                }
+                // staging buffer grp & 1: the store issued from it two groups ago must have read it out
+                unsigned char* stage = smem + Sh::OFF_OUT + (grp & 1) * Sh::OUT_BYTES;
+                if (issuer) dme::store_wait_read<1>();
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                #pragma unroll
+                for (int ch = 0; ch < 8; ++ch)                  // row r, 16-byte chunk ch, 128-byte swizzle
+                    *reinterpret_cast<uint4*>(stage + swz128(r, ch)) = make_uint4(w[4 * ch], w[4 * ch + 1], w[4 * ch + 2], w[4 * ch + 3]);
+                dme::fence_proxy_async_smem();
+                asm volatile("bar.sync 2, 128;" ::: "memory");
+                if (issuer) {
+                    if (EPI == GEMM_EPI_ACC32) dme::reduce_add_tile_2d(&mapC, tn * OUT_N + c * GCOLS, tm * kTM, stage);
+                    else                       dme::store_tile_2d(&mapC, tn * OUT_N + c * GCOLS, tm * kTM, stage);
+                    dme::store_commit();
                 }
             }
             tc::fence_before_sync();
             dme::mbar_arrive(&acc_empty[b]);
         }
+        if (issuer) dme::store_wait_all();
     }
     if (!ok) atomicExch(&s_failed, 1);
     tc::fence_before_sync();
@@ -247,6 +239,12 @@ int launch_gemm(const void* A, const void* W, void* C, int M, int N, int K, long
     const uint32_t boxa[2] = {kTK, kTM}, boxw[2] = {kTK, 128};
     cudaError_t e = make_tensor_map(&ma, dt, 2, A, ad, as, boxa, Swizzle::B128);
     if (e == cudaSuccess) e = make_tensor_map(&mw, dt, 2, W, wd, ws, boxw, Swizzle::B128);
+    // C: boxes of 128 rows x 128 bytes, written (or add-reduced) from the epilogue's staging tiles
+    constexpr bool OUT16 = EPI == GEMM_EPI_STORE16 || EPI == GEMM_EPI_SILU16;
+    CUtensorMap mc;
+    const uint64_t cd[2] = {uint64_t(N), uint64_t(M)}, cs[1] = {uint64_t(ldc) * (OUT16 ? 2 : 4)};
+    const uint32_t boxc[2] = {OUT16 ? 64u : 32u, kTM};
+    if (e == cudaSuccess) e = make_tensor_map(&mc, OUT16 ? dt : CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, C, cd, cs, boxc, Swizzle::B128);
     if (e != cudaSuccess) return int(e);
     auto kern = gemm_tc_kernel<T, BN, EPI>;
     static bool attr_set[64] = {};
@@ -266,7 +264,7 @@ int launch_gemm(const void* A, const void* W, void* C, int M, int N, int K, long
     p.abort_word = slot.abort;
     const long long tiles = (long long)p.tiles_m * p.tiles_n;
     const int sms = sm_count();
-    kern<<<unsigned(tiles < sms ? tiles : sms), kGemmThreads, Sh::SMEM_BYTES, st>>>(p, ma, mw);
+    kern<<<unsigned(tiles < sms ? tiles : sms), kGemmThreads, Sh::SMEM_BYTES, st>>>(p, ma, mw, mc);
     return launched();
 }
 
@@ -274,10 +272,14 @@ template <typename T, int EPI>
 int launch_gemm_bn(const void* A, const void* W, void* C, int M, int N, int K, long long lda, long long ldw, long long ldc,
                    int dtype, cudaStream_t st) {
     if (EPI == GEMM_EPI_SILU16) return launch_gemm<T, 256, EPI>(A, W, C, M, N, K, lda, ldw, ldc, dtype, st);
-    // wide tiles read less shared memory per flop; narrow tiles when the wide ones would leave SMs without work
-    const long long wide = (long long)((M + kTM - 1) / kTM) * ((N + 255) / 256);
+    // A 128 x 256 tile moves 1.5 bytes of shared memory per flop-unit against 2 for a 128 x 128 tile (both the TMA
+    // writes and the MMA reads share the 128 bytes per clock of an SM), so per column it costs 3/4 of the narrow
+    // tile's time; but the launch takes whole waves of tiles over the SMs.  Pick the width with the smaller
+    // waves x time-per-tile (narrow tile = 2 units, wide = 3).
+    const long long tm = (M + kTM - 1) / kTM, sms = sm_count();
+    const long long waves128 = (tm * ((N + 127) / 128) + sms - 1) / sms, waves256 = (tm * ((N + 255) / 256) + sms - 1) / sms;
     const int forced = tuning(KNOB_GEMM_TILE_N, 0);
-    const bool use_wide = forced == 256 || (forced != 128 && wide >= sm_count());
+    const bool use_wide = forced == 256 || (forced != 128 && 3 * waves256 <= 2 * waves128);
     return use_wide ? launch_gemm<T, 256, EPI>(A, W, C, M, N, K, lda, ldw, ldc, dtype, st)
                     : launch_gemm<T, 128, EPI>(A, W, C, M, N, K, lda, ldw, ldc, dtype, st);
 }
@@ -301,11 +303,11 @@ int gemm_tc(int dtype, int epi, const void* A, const void* W, void* C, int M, in
     if (!A || !W || !C) return B200P_E_NULL;
     if (dtype != B200P_F16 && dtype != B200P_BF16) return B200P_E_DTYPE;
     if (M <= 0 || N <= 0 || K <= 0) return B200P_E_LENGTH;
-    // TMA: 16-byte aligned bases and row strides; the epilogue's 32-byte stores need rows of C on 32 bytes
+    // TMA: 16-byte aligned bases and row strides for A, W and C
     if (K % 8 != 0 || lda % 8 != 0 || ldw % 8 != 0 || lda < K || ldw < K || ldc < N) return B200P_E_RANGE;
-    if (!aligned(A, 16) || !aligned(W, 16) || !aligned(C, 32)) return B200P_E_ALIGN;
+    if (!aligned(A, 16) || !aligned(W, 16) || !aligned(C, 16)) return B200P_E_ALIGN;
     const bool c16 = epi == GEMM_EPI_STORE16 || epi == GEMM_EPI_SILU16;
-    if ((ldc * (c16 ? 2 : 4)) % 32 != 0) return B200P_E_ALIGN;
+    if ((ldc * (c16 ? 2 : 4)) % 16 != 0) return B200P_E_ALIGN;
     if (sm_count() <= 0) return B200P_E_NO_DEVICE;
     return dtype == B200P_F16 ? launch_gemm_epi<__half>(epi, A, W, C, M, N, K, lda, ldw, ldc, dtype, st)
                               : launch_gemm_epi<__nv_bfloat16>(epi, A, W, C, M, N, K, lda, ldw, ldc, dtype, st);

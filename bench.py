@@ -67,7 +67,7 @@ class ClockSampler:
     REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown",
                0x40: "hw_thermal_slowdown", 0x80: "hw_power_brake_slowdown"}
 
-    def __init__(self, index: int, period: float = 0.002):
+    def __init__(self, index: int, period: float = 0.0):       # 0: back-to-back NVML queries (each takes about a millisecond)
         self.index, self.period = index, period
         self.samples, self.reasons = [], set()
         self.max_mhz = None
@@ -93,7 +93,8 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            time.sleep(self.period)
+            if self.period > 0:
+                time.sleep(self.period)
 
     def __enter__(self):
         if self.nv is not None:

@@ -119,8 +119,8 @@ int b200p_skinny_gemm(int dtype, int prologue, int epilogue, const void* W, cons
  * kernel that follows each GEMM in the reference folded into the epilogue:
  *   epilogue 0: C 16-bit;  2: C fp32;  1: C fp32 += product (the residual add, forward.hpp add_f32_kernel);
  *   epilogue 3: W is [2N, K] (gate rows, then up rows), C 16-bit = SiLU(gate) * up (forward.hpp:154-160).
- * A [M, lda] and W [N, ldw] 16-bit, row-major; lda, ldw, K multiples of 8; A, W 16-byte and C 32-byte aligned
- * with rows of C on 32 bytes.  B200P_E_RANGE / B200P_E_ALIGN for anything else (nothing is launched). */
+ * A [M, lda] and W [N, ldw] 16-bit, row-major; lda, ldw, K multiples of 8; A, W, C and the rows of C 16-byte
+ * aligned.  B200P_E_RANGE / B200P_E_ALIGN for anything else (nothing is launched). */
 int b200p_gemm_16(int dtype, int epilogue, const void* A, const void* W, void* C, int M, int N, int K,
                   long long lda, long long ldw, long long ldc, b200p_stream_t stream);
 

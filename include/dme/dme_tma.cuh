@@ -115,6 +115,28 @@ __device__ __forceinline__ void copy_tile_4d_stream(void* smem_dst, const void* 
     asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5, %6}], [%2], %7;"
                  :: "r"(smem_addr(smem_dst)), "l"(tensor_map), "r"(smem_addr(bar)), "r"(x), "r"(y), "r"(z), "r"(w), "l"(policy) : "memory");
 }
+// ---- shared -> global tile stores (issued by ONE thread, completion tracked in bulk groups) -----------
+// The box at element coordinates (x, y) of the tensor map is written from a dense (swizzled as the map says)
+// shared-memory tile; rows and columns outside the tensor are clipped by the hardware.  x * element size must
+// be a multiple of 16 bytes and no coordinate may be negative.  Make the generic-proxy writes of the tile
+// visible first (fence_proxy_async_smem + a barrier over the writing threads).
+__device__ __forceinline__ void store_tile_2d(const void* tensor_map, int x, int y, const void* smem_src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"(tensor_map), "r"(smem_addr(smem_src)), "r"(x), "r"(y) : "memory");
+}
+// The same with an fp32 add into global memory instead of a plain write (every element of the box is
+// read-modified-written once, in L2).
+__device__ __forceinline__ void reduce_add_tile_2d(const void* tensor_map, int x, int y, const void* smem_src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];"
+                 :: "l"(tensor_map), "r"(smem_addr(smem_src)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Wait until at most N of this thread's committed store groups still READ their shared-memory source
+// (the source of the older ones may be overwritten) ...
+template <int N> __device__ __forceinline__ void store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" :: "n"(N) : "memory"); }
+// ... and until all of them have completed.
+__device__ __forceinline__ void store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
 __device__ __forceinline__ void prefetch_tensor_map(const void* tensor_map) {
     asm volatile("prefetch.tensormap [%0];" :: "l"(tensor_map) : "memory");
 }

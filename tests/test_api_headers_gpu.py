@@ -62,9 +62,9 @@ def test_register_resident_reduce_loop(b200p, torch_cuda, dt, backend):
         got = b200p.wave_reduce_loop(x, op, reps, backend)
         v, acc = x.view(waves, 64).clone(), torch.zeros(waves, device="cuda", dtype=dtype)
         for _ in range(reps):
-            s = fn(v)
+            s = fn(v).to(dtype)                                 # the kernel's arithmetic wraps in the element type
             acc = acc + s
-            v = s[:, None] + lane[None, :]
+            v = (s[:, None] + lane[None, :]).to(dtype)
         assert torch.equal(got, acc), (dt, op)
 
 

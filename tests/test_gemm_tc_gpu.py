@@ -27,7 +27,7 @@ def test_store_and_accumulate(b200p, torch_cuda, M, N, K, kind, tile_n):
     A, W, dt = ops(torch, M, N, K, kind, M + N + K)
     ref = A.double() @ W.double().T
     scale = max(1.0, ref.abs().max().item())
-    ldc16, ldc32 = -(-N // 16) * 16, -(-N // 8) * 8                  # rows of C on 32 bytes
+    ldc16, ldc32 = -(-N // 8) * 8 + 8, -(-N // 4) * 4 + 4               # rows of C on 16 bytes, a little wider than N
     b200p.set_tuning("gemm_tile_n", tile_n)
     try:
         c16 = torch.zeros(M, ldc16, dtype=dt, device="cuda")
@@ -55,7 +55,7 @@ def test_silu_gate_up_epilogue(b200p, torch_cuda, M, F, K, kind):
     A, W, dt = ops(torch, M, F, K, kind, F, wrows=2 * F)
     g, u = A.double() @ W[:F].double().T, A.double() @ W[F:].double().T
     ref = g / (1.0 + torch.exp(-g)) * u
-    ldc = -(-F // 16) * 16
+    ldc = -(-F // 8) * 8 + 8
     out = torch.zeros(M, ldc, dtype=dt, device="cuda")
     b200p.gemm_16(A, W, out[:, :F], "silu16")
     assert b200p.device_status() == 0
@@ -75,7 +75,7 @@ def test_domain_errors(b200p, torch_cuda):
     assert e.value.status == -10 and b200p.launch_count() == n0
     A = torch.zeros(64, 64, dtype=torch.bfloat16, device="cuda")
     with pytest.raises(b200p.B200PError) as e:
-        b200p.gemm_16(A, A, torch.zeros(64, 72, dtype=torch.bfloat16, device="cuda")[:, :64])   # rows of C not on 32 bytes
+        b200p.gemm_16(A, A, torch.zeros(64, 68, dtype=torch.bfloat16, device="cuda")[:, :64])   # rows of C not on 16 bytes
     assert e.value.status == -5
 
 
