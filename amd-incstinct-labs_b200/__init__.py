@@ -604,7 +604,7 @@ class Session:
         self._device = weights["embed_tokens"].device
 
     def close(self):
-        if getattr(self, "_h", None):
+        if getattr(self, "_h", None) and lib is not None:        # `lib` is gone when the interpreter is shutting down
             lib().b200p_session_destroy(self._h)
             self._h = None
 
