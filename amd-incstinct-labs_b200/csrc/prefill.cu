@@ -25,7 +25,7 @@
 //                 32x32b gives a thread its whole row, so row max and row sum need
 //                 no cross-lane step at all), exp2 with the scale folded in, lazy
 //                 rescaling of O (only when the running max grew by more than 2^8),
-//                 final O / l and the store.
+//                 final O / l and the store (swizzled staging tile + TMA store).
 // All barrier phases run on from one item to the next, so the next item's Q, K_0 and
 // first Q.K^T are in flight while the softmax warps normalise and store the previous
 // item's O (measured per item: 18.5k cycles of fill, drain and launch with one CTA per
@@ -66,19 +66,17 @@ template <int D> struct PrefillShape {
     static constexpr int OFF_Q = 0;
     static constexpr int OFF_K = 2 * TILE_BYTES;
     static constexpr int OFF_V = OFF_K + KSTAGES * TILE_BYTES;
-    static constexpr int OFF_BAR = OFF_V + VSTAGES * TILE_BYTES;
+    static constexpr int OFF_OUT = OFF_V + VSTAGES * TILE_BYTES;   // one [128 rows][128 B] staging tile per query tile (epilogue)
+    static constexpr int OFF_BAR = OFF_OUT + 2 * SUB_BYTES;
     static constexpr int SMEM_BYTES = OFF_BAR + 1024;
 };
 
 struct PrefillParams {
-    void* O;
-    long long o_seq, o_head, o_batch;   // element strides of O
     float* debug_s;            // optional: raw S of tile (0,0) of CTA (0,0,0), [128][128] fp32
     int* status;               // this launch's abort word: raised by a wait that gave up, polled by all its waits
     int* sticky;               // the library's sticky status word, raised at exit by a CTA that saw a failed wait
     int* work_counter;         // zero at launch: the CTAs draw the ids of their later work items from it
     int seqQ, seqK, nQH, nKVH, group, batch, causal;
-    int o_vec32;               // O and all of its strides are multiples of 32 bytes: the epilogue stores whole sectors
     float scale_log2;
 };
 
@@ -115,7 +113,8 @@ __device__ __forceinline__ PrefillItem prefill_item(const PrefillParams& p, int 
 template <typename T, int D, int RS, bool DBG>
 __global__ void __launch_bounds__(prefill_threads(RS), 1)
 prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap mapQ,
-                  const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV) {
+                  const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+                  const __grid_constant__ CUtensorMap mapO) {
     using Sh = PrefillShape<D>;
     constexpr int KST = Sh::KSTAGES, VST = Sh::VSTAGES;
     extern __shared__ __align__(1024) unsigned char smem[];
@@ -312,9 +311,22 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
         const uint32_t tO = tmem + lane_base + 256u + uint32_t(t * 128) + uint32_t(half * OW);
         int cs = 0, co = 0;                                    // as in the MMA thread, for this tile
         bool ok = true;
-        for (int it = 0; ok; ++it) {
+        // The tile's 128 threads meet at named barrier 2 + t in the epilogue, so they leave this loop TOGETHER: whether a
+        // thread's waits of an item all succeeded is and-reduced over the warpgroup (a barrier every one of them reaches,
+        // once per item) before anyone acts on it.
+        auto all_of_tile = [&](bool mine) -> bool {
+            uint32_t r_;
+            asm volatile("{\n\t.reg .pred p, q;\n\tsetp.ne.u32 q, %1, 0;\n\tbarrier.cta.red.and.pred p, %2, 128, q;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                         : "=r"(r_) : "r"(uint32_t(mine)), "r"(2 + t) : "memory");
+            return r_ != 0;
+        };
+        auto tile_sync = [&]() { asm volatile("bar.sync %0, 128;" :: "r"(2 + t) : "memory"); };
+        const bool issuer = r == 0;                            // issues and tracks this tile's output stores
+        unsigned char* stage = smem + Sh::OFF_OUT + t * Sh::SUB_BYTES;
+        if (issuer) dme::prefetch_tensor_map(&mapO);
+        for (int it = 0;; ++it) {
           const int id = next_item(it);
-          if (id < 0) { ok = id != -2; break; }
+          if (id < 0) { ok = all_of_tile(id != -2); break; }   // -1: the launch's items are used up (the same value in every thread)
           const PrefillItem w = prefill_item(p, id);
           const int q0t = t ? w.q0[1] : w.q0[0], nt = t ? w.n[1] : w.n[0];     // no arrays indexed at run time
           const int o_b = w.b, o_head = w.head;
@@ -391,11 +403,12 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             }
             l = l * alpha + ((la[0] + la[1]) + (la[2] + la[3]));
           }
+          // ---- epilogue: O / l -> 16-bit, through a swizzled staging tile and TMA stores (64 columns at a time).  O is taken
+          // into registers first and the tile's tensor memory released, so the next item's P.V does not wait for the stores.
+          if (ok && nt > 0) ok = dme::wait(&o_done[t], uint32_t(co & 1), p.status);
+          ok = all_of_tile(ok);
           if (!ok) break;
-          // ---- epilogue: O / l -> 16-bit; a thread writes its OW output columns of its row.  O is taken into
-          // registers first and the tile's tensor memory released, so the next item's P.V does not wait for the stores.
           if (nt > 0) {
-            if (!dme::wait(&o_done[t], uint32_t(co & 1), p.status)) { ok = false; break; }
             tc::fence_after_sync();
             uint32_t v[OW];
             #pragma unroll
@@ -403,34 +416,32 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
             tc::wait_ld();
             tc::fence_before_sync();
             dme::mbar_arrive(&o_free[t]);
-            if (row < p.seqQ) {
-                const float inv = l > 0.f ? 1.f / l : 1.f;
-                T* orow = static_cast<T*>(p.O) + size_t(o_b) * p.o_batch + size_t(o_head) * p.o_head + size_t(row) * p.o_seq + half * OW;
-                // 32-byte stores (whole sectors) where the rows of O allow them, else 16-byte stores
-                if (p.o_vec32) {
+            const float inv = l > 0.f ? 1.f / l : 1.f;
+            #pragma unroll
+            for (int hb = 0; hb < D / 64; ++hb) {
+                if (issuer) dme::store_wait_read<0>();           // the previous store from this staging tile has read it out
+                tile_sync();
                 #pragma unroll
-                for (int q16 = 0; q16 < OW / 16; ++q16) {
-                    uint32_t o8[8];
-                    #pragma unroll
-                    for (int u = 0; u < 8; ++u) o8[u] = pack2<T>(__uint_as_float(v[q16 * 16 + 2 * u]) * inv, __uint_as_float(v[q16 * 16 + 2 * u + 1]) * inv);
-                    asm volatile("st.global.v8.b32 [%8], {%0,%1,%2,%3,%4,%5,%6,%7};"
-                                 :: "r"(o8[0]), "r"(o8[1]), "r"(o8[2]), "r"(o8[3]), "r"(o8[4]), "r"(o8[5]), "r"(o8[6]), "r"(o8[7]), "l"(orow + q16 * 16) : "memory");
-                }
-                } else {
-                #pragma unroll
-                for (int q8 = 0; q8 < OW / 8; ++q8) {
+                for (int ch = 0; ch < 8; ++ch) {                 // row r, 16-byte chunk ch, 128-byte swizzle
+                    const int c0 = hb * 64 + ch * 8;
                     uint4 o4;
-                    o4.x = pack2<T>(__uint_as_float(v[q8 * 8 + 0]) * inv, __uint_as_float(v[q8 * 8 + 1]) * inv);
-                    o4.y = pack2<T>(__uint_as_float(v[q8 * 8 + 2]) * inv, __uint_as_float(v[q8 * 8 + 3]) * inv);
-                    o4.z = pack2<T>(__uint_as_float(v[q8 * 8 + 4]) * inv, __uint_as_float(v[q8 * 8 + 5]) * inv);
-                    o4.w = pack2<T>(__uint_as_float(v[q8 * 8 + 6]) * inv, __uint_as_float(v[q8 * 8 + 7]) * inv);
-                    *reinterpret_cast<uint4*>(orow + q8 * 8) = o4;
+                    o4.x = pack2<T>(__uint_as_float(v[c0 + 0]) * inv, __uint_as_float(v[c0 + 1]) * inv);
+                    o4.y = pack2<T>(__uint_as_float(v[c0 + 2]) * inv, __uint_as_float(v[c0 + 3]) * inv);
+                    o4.z = pack2<T>(__uint_as_float(v[c0 + 4]) * inv, __uint_as_float(v[c0 + 5]) * inv);
+                    o4.w = pack2<T>(__uint_as_float(v[c0 + 6]) * inv, __uint_as_float(v[c0 + 7]) * inv);
+                    *reinterpret_cast<uint4*>(stage + swz128(r, ch)) = o4;
                 }
+                dme::fence_proxy_async_smem();
+                tile_sync();
+                if (issuer) {                                    // rows past seqQ are clipped by the tensor map
+                    dme::store_tile_4d(&mapO, hb * 64, q0t, o_head, o_b, stage);
+                    dme::store_commit();
                 }
             }
           }
           cs += nt; co += nt > 0;
         }
+        if (issuer) dme::store_wait_all();
         if (!ok) atomicExch(&s_failed, 1);
     }
     tc::fence_before_sync();
@@ -455,6 +466,9 @@ int launch_prefill_rs(const void* Q, const void* K, const void* V, void* O, cons
     cudaError_t e = make_tensor_map(&mq, dt, 4, Q, qd, qs, box, Swizzle::B128);
     if (e == cudaSuccess) e = make_tensor_map(&mk, dt, 4, K, kd, ks, box, Swizzle::B128);
     if (e == cudaSuccess) e = make_tensor_map(&mv, dt, 4, V, kd, vs, box, Swizzle::B128);
+    CUtensorMap mo;
+    const uint64_t os[3] = {uint64_t(s.o_seq) * 2, uint64_t(s.o_head) * 2, uint64_t(s.o_batch) * 2};
+    if (e == cudaSuccess) e = make_tensor_map(&mo, dt, 4, O, qd, os, box, Swizzle::B128);
     if (e != cudaSuccess) return int(e);
 
     const bool dbg = debug_s != nullptr;
@@ -467,14 +481,12 @@ int launch_prefill_rs(const void* Q, const void* K, const void* V, void* O, cons
         attr_set[dev][dbg] = true;
     }
     PrefillParams p{};
-    p.O = O; p.debug_s = debug_s;
+    p.debug_s = debug_s;
     p.sticky = device_status_ptr();
     LaunchSlot slot{};
     if (!p.sticky) return B200P_E_NO_DEVICE;
     if (int se = take_launch_slot(st, &slot)) return se;       // work counter and abort word of this launch, cleared on its stream
     p.status = slot.abort; p.work_counter = slot.work;
-    p.o_seq = s.o_seq; p.o_head = s.o_head; p.o_batch = s.o_batch;
-    p.o_vec32 = aligned(O, 32) && s.o_seq % 16 == 0 && s.o_head % 16 == 0 && s.o_batch % 16 == 0;
     p.seqQ = c->seqQ; p.seqK = c->seqK; p.nQH = c->nQHeads; p.nKVH = c->nKVHeads; p.group = c->nQHeads / c->nKVHeads;
     p.batch = c->batch; p.causal = c->causal;
     p.scale_log2 = 1.4426950408889634f / sqrtf(float(D));
@@ -485,7 +497,7 @@ int launch_prefill_rs(const void* Q, const void* K, const void* V, void* O, cons
     const int sms = sm_count();
     const bool one_per_item = (tuning(KNOB_PREFILL_VARIANT, 0) & 2) != 0;
     dim3 grid(unsigned(one_per_item || items < sms ? items : sms), 1, 1);
-    kern<<<grid, prefill_threads(RS), Sh::SMEM_BYTES, st>>>(p, mq, mk, mv);
+    kern<<<grid, prefill_threads(RS), Sh::SMEM_BYTES, st>>>(p, mq, mk, mv, mo);
     return launched();
 }
 

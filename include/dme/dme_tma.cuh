@@ -124,6 +124,10 @@ __device__ __forceinline__ void store_tile_2d(const void* tensor_map, int x, int
     asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%2, %3}], [%1];"
                  :: "l"(tensor_map), "r"(smem_addr(smem_src)), "r"(x), "r"(y) : "memory");
 }
+__device__ __forceinline__ void store_tile_4d(const void* tensor_map, int x, int y, int z, int w, const void* smem_src) {
+    asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+                 :: "l"(tensor_map), "r"(smem_addr(smem_src)), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
 // The same with an fp32 add into global memory instead of a plain write (every element of the box is
 // read-modified-written once, in L2).
 __device__ __forceinline__ void reduce_add_tile_2d(const void* tensor_map, int x, int y, const void* smem_src) {
