@@ -54,6 +54,10 @@ constexpr int kBN = 128;                 // keys per tile
 // warps (tile, lane quarter), the next warpgroup holds the MMA and the TMA warp.
 constexpr int prefill_threads(int RS) { return (8 * RS + 4) * 32; }
 constexpr float kLazyRescale = 8.0f;     // log2 units
+// P is handed to the MMA warp in two parts: the first kFirstChunks 32-key chunks of a tile as soon as they are stored,
+// then the rest; only the second part's P.V stands between the end of the softmax and the next Q.K^T.
+// (Measured: 1, 2 or 3 chunks first make no difference beyond run-to-run noise.)
+constexpr int kFirstChunks = 2;
 // The debug instantiation (DBG, used by b200p_attn_prefill_debug only) writes the raw scores of the first
 // tile to the debug buffer; the production instantiation does not carry that code.
 
@@ -236,10 +240,10 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                     tc::mma_ss(tmem + t * kBN, qd + off16, kd + off16, idesc_qk, ks > 0);
                 }
             };
-            auto issue_pv = [&](int t, int vstage, bool first, int kk0) {          // half of the keys: kk0 .. kk0+3
+            auto issue_pv = [&](int t, int vstage, bool first, int kk0, int kk1) {  // 16-key steps kk0 .. kk1-1 of the tile
                 const uint64_t vd = v_base + uint64_t((vstage * Sh::TILE_BYTES) >> 4);
                 #pragma unroll
-                for (int kk = kk0; kk < kk0 + kBN / 32; ++kk)
+                for (int kk = kk0; kk < kk1; ++kk)
                     tc::mma_ts(tmem + 256 + t * 128, tmem + t * kBN + kk * 8, vd + uint64_t(kk * (2048 >> 4)),
                                idesc_pv, !(first && kk == 0));
             };
@@ -269,10 +273,10 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                     // the first P.V of an item overwrites O_t: the previous item's epilogue must have read it
                     if (j == 0 && cot > 0 && !dme::wait(&o_free[t], uint32_t((cot - 1) & 1), p.status)) return false;
                     tc::fence_after_sync();
-                    issue_pv(t, vr.stage, j == 0, 0);                 // keys 0..63 while the softmax finishes 64..127
+                    issue_pv(t, vr.stage, j == 0, 0, 2 * kFirstChunks);   // the first hand-off's keys while the softmax finishes the rest
                     if (!dme::wait(&p_half[2 * t + 1], uint32_t((cst + j) & 1), p.status)) return false;
                     tc::fence_after_sync();
-                    issue_pv(t, vr.stage, j == 0, kBN / 32);
+                    issue_pv(t, vr.stage, j == 0, 2 * kFirstChunks, kBN / 16);
                     if (j + 1 < nt) { issue_qk(t, kr.stage); tc::commit(&s_full[t]); }
                     else tc::commit(&o_done[t]);
                     return true;
@@ -389,10 +393,10 @@ prefill_tc_kernel(const PrefillParams p, const __grid_constant__ CUtensorMap map
                 }
                 tc::st_32x32b_x16(tS + (half * CW) / 2 + c * 16, pk);
                 const int key_chunk = half * (CW / 32) + c;                   // 32-key chunk of the tile: 0..3
-                if (key_chunk == 1 || key_chunk == 3) {
+                if (key_chunk == kFirstChunks - 1 || key_chunk == 3) {
                     tc::wait_st();
                     tc::fence_before_sync();
-                    dme::mbar_arrive(&p_half[2 * t + (key_chunk >> 1)]);
+                    dme::mbar_arrive(&p_half[2 * t + (key_chunk == 3)]);
                 }
             }
             float la[4] = {0.f, 0.f, 0.f, 0.f};

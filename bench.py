@@ -1064,8 +1064,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
-    ap.add_argument("--workload", default="all", choices=sorted(WORKLOADS) + ["all"],
-                    help="all = prefill (headline) with the other five reported under 'others'")
+    ap.add_argument("--workload", default="all",
+                    help="all = prefill (headline) with the others reported under 'others'; or one name, or a comma-separated "
+                         "list of names (the first is the headline): " + ", ".join(sorted(WORKLOADS)))
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--e2e-steps", type=int, default=None, help="steps of the host-buffer (end-to-end) measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -1079,7 +1080,10 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    names = ALL_ORDER if args.workload == "all" else [args.workload]
+    names = ALL_ORDER if args.workload == "all" else [w.strip() for w in args.workload.split(",") if w.strip()]
+    for w in names:
+        if w not in WORKLOADS:
+            ap.error(f"unknown workload {w!r}")
     # stdout must carry exactly ONE JSON line: libraries that chat on file descriptor 1
     # (NCCL prints its version there) are pointed at stderr; the line goes to the saved descriptor.
     sys.stdout.flush()
