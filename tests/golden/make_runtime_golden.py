@@ -27,7 +27,8 @@ PROMPT_LEN, MAX_NEW = 40, 12
 
 
 def main():
-    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("B200P_REFERENCE_ROOT", "")
+    repo = os.path.dirname(os.path.dirname(HERE))
+    root = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("B200P_REFERENCE_ROOT", os.path.join(os.path.dirname(repo), "reference"))
     exporter = os.path.join(root, "cdna3-prims", "runtime", "export_model.py")
     if not os.path.exists(exporter):
         raise SystemExit("reference tree not found: pass its root as argv[1] or in B200P_REFERENCE_ROOT")
