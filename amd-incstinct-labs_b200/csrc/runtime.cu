@@ -307,7 +307,7 @@ int ensure_scratch(b200p_session* s, int Tn, int max_new) {
 bool skinny_ok(const b200p_session* s, int M) {
     const auto& c = s->c;
     return tuning(KNOB_RUNTIME_SKINNY, 2) != 0 && s->skinny_aligned && M <= kSkinnyMaxM && c.hidden % 16 == 0 && c.ffn_dim % 16 == 0 &&
-           s->qd % 16 == 0 && size_t(8) * size_t(c.ffn_dim > c.hidden ? c.ffn_dim : c.hidden) * 2 <= 200 * 1024;
+           s->qd % 16 == 0 && size_t(M <= 8 ? 8 : 16) * size_t((c.ffn_dim > c.hidden ? c.ffn_dim : c.hidden) + kSkinnyXPad) * 2 <= 190 * 1024;
 }
 
 // One decoder layer of the decode step (one new token per sequence) on the skinny kernels:

@@ -1,5 +1,5 @@
 // ---------------------------------------------------------------------------
-// skinny_gemm.cuh -- Y[M,N] = X[M,K] . W[N,K]^T for the decode step (M <= 8 rows).
+// skinny_gemm.cuh -- Y[M,N] = X[M,K] . W[N,K]^T for the decode step (M <= 16 rows).
 //
 // At decode time the reference runs every projection as a rocBLAS GEMM with
 // M = batch (cdna3-prims/include/cdna3/runtime/rocblas_gemm.hpp:112-209) between
@@ -18,8 +18,10 @@
 //    ARE its A fragments: within a 64-wide block, lane t4 of a row's four lanes
 //    supplies columns 16*t4 + 4s .. +3 to k-step s, and reads the same columns
 //    of X for the B fragment.  No unpacking, no shuffles: 4 MMAs per 2 KB of W.
-//  * X (16-bit, M rounded up to 1, 2, 4 or 8 rows) sits in shared memory with rows 16 bytes
-//    longer than K, which makes the 16-byte fragment reads bank-conflict free.
+//  * X (16-bit, M rounded up to 1, 2, 4, 8 or 16 rows) sits in shared memory with rows 16 bytes
+//    longer than K, which makes the 16-byte fragment reads bank-conflict free.  Up to 8 rows of X
+//    are the 8 columns of ONE B fragment; rows 8..15 are a second B fragment and a second MMA
+//    per A fragment (template parameter MH = 2), so the weights are still read once.
 //  * Prologue PRO_RMSNORM computes the RMSNorm of the fp32 residual stream
 //    straight into shared memory (all 8 warps, values held in registers between
 //    the sum of squares and the scaling): the norm kernel and its 16-bit round
@@ -86,7 +88,7 @@ struct SkinnyArgs {
 
 constexpr int kSkinnyThreads = 256;
 constexpr int kSkinnyWarps = kSkinnyThreads / 32;
-constexpr int kSkinnyMaxM = 8;
+constexpr int kSkinnyMaxM = 16;
 constexpr int kSkinnyDepth = 4;       // 64-column blocks in flight per warp
 constexpr int kSkinnyXPad = 8;        // elements: X rows are 16 bytes longer than K
 
@@ -99,7 +101,34 @@ template <typename T, int PRO>
 __device__ __forceinline__ void skinny_prologue(const SkinnyArgs& a, T* xs, float* part_ss, int Mp, int warp, int lane) {
     const int K = a.K, xstride = K + kSkinnyXPad;
     // ---- prologue: X into shared memory as 16-bit, rows in [M, Mp) zero --------------------------------
-    if (PRO == PRO_RMSNORM) {
+    if (PRO == PRO_RMSNORM && Mp > kSkinnyWarps) {
+        // more rows than warps (Mp = 16): a warp normalises rows warp and warp + 8, one after the other
+        const T* nw = static_cast<const T*>(a.norm_w);
+        for (int m = warp; m < Mp; m += kSkinnyWarps) {
+            T* dst = xs + size_t(m) * xstride;
+            if (m < a.M) {
+                const float* x = a.X32 + size_t(m) * K;
+                float ss = 0.f;
+                for (int q = lane; q < K / 4; q += 32) {
+                    const float4 v = *reinterpret_cast<const float4*>(x + 4 * q);
+                    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+                }
+                ss = wave::dpp::reduce_sum(ss);
+                const float inv = rsqrtf(ss / K + a.eps);
+                for (int q = lane; q < K / 4; q += 32) {
+                    const float4 v = *reinterpret_cast<const float4*>(x + 4 * q);
+                    const uint2 wv = *reinterpret_cast<const uint2*>(nw + 4 * q);
+                    const T* w4 = reinterpret_cast<const T*>(&wv);
+                    uint2 o;
+                    o.x = pack2<T>(v.x * inv * to_float(w4[0]), v.y * inv * to_float(w4[1]));
+                    o.y = pack2<T>(v.z * inv * to_float(w4[2]), v.w * inv * to_float(w4[3]));
+                    *reinterpret_cast<uint2*>(dst + 4 * q) = o;
+                }
+            } else {
+                for (int q = lane; q < K / 4; q += 32) *reinterpret_cast<uint2*>(dst + 4 * q) = make_uint2(0u, 0u);
+            }
+        }
+    } else if (PRO == PRO_RMSNORM) {
         // forward.hpp:34-56: y = x * rsqrt(mean(x^2) + eps) * w.  8 / Mp warps share a row; each keeps
         // up to 4 quads per lane in registers between the sum of squares and the scaling.
         constexpr int CACHE = 4;
@@ -166,15 +195,18 @@ __device__ __forceinline__ void skinny_prologue(const SkinnyArgs& a, T* xs, floa
 
 // The eight warps' partial accumulators (red[warp][lane][4]: the m16n8 C fragments) meet; the first 64 * R
 // threads write the group's outputs.  prev: for EPI_ACC32, the residual values fetched ahead (use_prev).
-template <typename T, int EPI, int R>
-__device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, const float (*red)[32][4], int grp, int tid, bool use_prev, float prev) {
+// red[warp][lane][4 * mh + c]: the m16n8 C fragment of the MMA over rows 8 mh .. 8 mh + 7 of X.
+template <typename T, int EPI, int R, int MH>
+__device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, const float (*red)[32][4 * MH], int grp, int tid, bool use_prev, float prev) {
+    #pragma unroll
+    for (int mh = 0; mh < MH; ++mh) {
         if (EPI == EPI_SILU16) {
             if (tid < 64) {
                 const int l = tid % 32, sel = tid / 32;
                 float gate = 0.f, up = 0.f;
                 #pragma unroll
-                for (int w = 0; w < kSkinnyWarps; ++w) { gate += red[w][l][sel]; up += red[w][l][2 + sel]; }
-                const int m = 2 * (l % 4) + sel, p = grp * 8 + l / 4;
+                for (int w = 0; w < kSkinnyWarps; ++w) { gate += red[w][l][4 * mh + sel]; up += red[w][l][4 * mh + 2 + sel]; }
+                const int m = 8 * mh + 2 * (l % 4) + sel, p = grp * 8 + l / 4;
                 if (m < a.M && p < a.N)
                     static_cast<T*>(a.out)[size_t(m) * a.ldo + p] = from_float<T>((gate / (1.f + expf(-gate))) * up);
             }
@@ -184,8 +216,8 @@ __device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, const float
                 const int l = tid % 32, sel = tid / 32;
                 float x0 = 0.f, x1 = 0.f;
                 #pragma unroll
-                for (int w = 0; w < kSkinnyWarps; ++w) { x0 += red[w][l][sel]; x1 += red[w][l][2 + sel]; }
-                const int m = 2 * (l % 4) + sel;
+                for (int w = 0; w < kSkinnyWarps; ++w) { x0 += red[w][l][4 * mh + sel]; x1 += red[w][l][4 * mh + 2 + sel]; }
+                const int m = 8 * mh + 2 * (l % 4) + sel;
                 if (m < a.M) {
                     const int cph = r.D / 16, half = r.D / 2;
                     const int slot = grp / cph, d = (grp % cph) * 8 + l / 4;
@@ -217,35 +249,36 @@ __device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, const float
             const int l = tid % 32, c = tid / 32;
             float v = 0.f;
             #pragma unroll
-            for (int w = 0; w < kSkinnyWarps; ++w) v += red[w][l][c];
-            const int m = 2 * (l % 4) + (c & 1), n = grp * 8 * R + l / 4 + 8 * (c >> 1);
+            for (int w = 0; w < kSkinnyWarps; ++w) v += red[w][l][4 * mh + c];
+            const int m = 8 * mh + 2 * (l % 4) + (c & 1), n = grp * 8 * R + l / 4 + 8 * (c >> 1);
             if (m < a.M && n < a.N) {
                 const size_t idx = size_t(m) * a.ldo + n;
                 if (EPI == EPI_STORE16)      static_cast<T*>(a.out)[idx] = from_float<T>(v);
                 else if (EPI == EPI_STORE32) static_cast<float*>(a.out)[idx] = v;
-                else if (use_prev) static_cast<float*>(a.out)[idx] = prev + v;
+                else if (use_prev && mh == 0) static_cast<float*>(a.out)[idx] = prev + v;
                 else                         static_cast<float*>(a.out)[idx] += v;
             }
         }
+    }
 }
 
 // R = rows of W per lane: 2 -> a CTA step covers 16 rows (accumulator rows g and g + 8), 4 column
 // blocks in flight; 1 -> 8 rows (the upper half of the A operand is zero), 8 blocks in flight: twice
 // the CTAs for matrices too small to fill the GPU otherwise.
-template <typename T, int PRO, int EPI, int R>
+template <typename T, int PRO, int EPI, int R, int MH>
 __global__ void __launch_bounds__(kSkinnyThreads, 2)
 skinny_gemm_kernel(const SkinnyArgs a) {
     griddep_launch_dependents();
     extern __shared__ __align__(128) unsigned char skinny_smem[];
     T* xs = reinterpret_cast<T*>(skinny_smem);                 // [Mp][K + pad]
-    __shared__ float red[2][kSkinnyWarps][32][4];               // double-buffered by group
+    __shared__ float red[2][kSkinnyWarps][32][4 * MH];          // double-buffered by group
     __shared__ float part_ss[kSkinnyWarps];
     constexpr int DEPTH = 8 / R;
     static_assert(R == 2 || (EPI != EPI_SILU16 && EPI != EPI_ROPE), "paired epilogues need both halves");
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int g = lane / 4, t4 = lane % 4;
     const int K = a.K, xstride = K + kSkinnyXPad;
-    const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;   // rows of X kept in shared memory
+    const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : a.M <= 8 ? 8 : 16;   // rows of X kept in shared memory
 
     // Row groups: group `grp` is 8 * R rows of W (8 row pairs for the paired epilogues); the CTA
     // takes groups blockIdx.x, blockIdx.x + gridDim.x, ...
@@ -315,24 +348,29 @@ skinny_gemm_kernel(const SkinnyArgs a) {
     const T* xrow = xs + size_t(g) * xstride + t4 * 16;        // B fragment: X row g, the lane's 16 columns
     int parity = 0;
     for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x, parity ^= 1) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc[MH][4];
+        #pragma unroll
+        for (int mh = 0; mh < MH; ++mh) { acc[mh][0] = acc[mh][1] = acc[mh][2] = acc[mh][3] = 0.f; }
         for (int jb = 0; jb < nb; jb += DEPTH) {
             #pragma unroll
             for (int d = 0; d < DEPTH; ++d) {
                 const int j = jb + d;
                 if (j < nb) {                                   // warp-uniform
                     const int blk = b0 + j;
-                    uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
-                    if (g < Mp && lane_live(blk)) {             // columns of B past Mp are zero: no row to read
-                        const uint4* xp = reinterpret_cast<const uint4*>(xrow + size_t(blk) * 64);
-                        xa = xp[0]; xb = xp[1];
-                    }
-                    const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
                     #pragma unroll
-                    for (int s = 0; s < 4; ++s) {
-                        const uint32_t af[4] = {wb[d][0][2 * s], R == 2 ? wb[d][R - 1][2 * s] : 0u,
-                                                wb[d][0][2 * s + 1], R == 2 ? wb[d][R - 1][2 * s + 1] : 0u};
-                        mma_16816<T>(acc, af, xw[2 * s], xw[2 * s + 1]);
+                    for (int mh = 0; mh < MH; ++mh) {
+                        uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
+                        if (g + 8 * mh < Mp && lane_live(blk)) {    // columns of B past Mp are zero: no row to read
+                            const uint4* xp = reinterpret_cast<const uint4*>(xrow + size_t(8 * mh) * xstride + size_t(blk) * 64);
+                            xa = xp[0]; xb = xp[1];
+                        }
+                        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                        #pragma unroll
+                        for (int s = 0; s < 4; ++s) {
+                            const uint32_t af[4] = {wb[d][0][2 * s], R == 2 ? wb[d][R - 1][2 * s] : 0u,
+                                                    wb[d][0][2 * s + 1], R == 2 ? wb[d][R - 1][2 * s + 1] : 0u};
+                            mma_16816<T>(acc[mh], af, xw[2 * s], xw[2 * s + 1]);
+                        }
                     }
                     // the slot is free: next block of this group that maps to it, else the next group's
                     if (j + DEPTH < nb) issue(d, grp, j + DEPTH);
@@ -342,9 +380,11 @@ skinny_gemm_kernel(const SkinnyArgs a) {
         }
 
         // ---- the 8 warps' partial sums meet; epilogue (the next group's loads are in flight) ---------
-        *reinterpret_cast<float4*>(&red[parity][warp][lane][0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+        #pragma unroll
+        for (int mh = 0; mh < MH; ++mh)
+            *reinterpret_cast<float4*>(&red[parity][warp][lane][4 * mh]) = make_float4(acc[mh][0], acc[mh][1], acc[mh][2], acc[mh][3]);
         skinny_barrier();
-        skinny_epilogue<T, EPI, R>(a, red[parity], grp, threadIdx.x, grp == int(blockIdx.x), prev);
+        skinny_epilogue<T, EPI, R, MH>(a, red[parity], grp, threadIdx.x, grp == int(blockIdx.x), prev);
     }
 }
 
@@ -365,12 +405,12 @@ skinny_gemm_kernel(const SkinnyArgs a) {
 constexpr int kSkinnySlab = 2048;                  // columns of W per stage
 constexpr int kSkinnyStreamThreads = kSkinnyThreads + 32;
 
-template <typename T, int PRO, int EPI>
+template <typename T, int PRO, int EPI, int MH>
 __global__ void __launch_bounds__(kSkinnyStreamThreads, 1)
 skinny_stream_kernel(const SkinnyArgs a, int nstages, int slab_cols, int* status, int* sticky) {
     griddep_launch_dependents();
     extern __shared__ __align__(128) unsigned char skinny_smem[];
-    __shared__ float red[2][kSkinnyWarps][32][4];
+    __shared__ float red[2][kSkinnyWarps][32][4 * MH];
     __shared__ float part_ss[kSkinnyWarps];
     __shared__ uint64_t bars[16];
     constexpr int kMaxStages = 8;
@@ -378,7 +418,7 @@ skinny_stream_kernel(const SkinnyArgs a, int nstages, int slab_cols, int* status
     uint64_t* empty_bar = bars + kMaxStages;
     const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
     const int K = a.K, xstride = K + kSkinnyXPad;
-    const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
+    const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : a.M <= 8 ? 8 : 16;
     const int slab = K < slab_cols ? K : slab_cols;               // columns per stage
     const int nslab = (K + slab - 1) / slab;
     const int rowb = slab * 2 + 16;                               // bytes between rows of a stage
@@ -430,7 +470,9 @@ skinny_stream_kernel(const SkinnyArgs a, int nstages, int slab_cols, int* status
         int parity = 0;
         bool ok = true;
         for (int grp = blockIdx.x; grp < ngroups; grp += gridDim.x, parity ^= 1) {
-            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            float acc[MH][4];
+            #pragma unroll
+            for (int mh = 0; mh < MH; ++mh) { acc[mh][0] = acc[mh][1] = acc[mh][2] = acc[mh][3] = 0.f; }
             for (int sl = 0; sl < nslab; ++sl) {
                 if (ok && !dme::wait(&full_bar[stage], phase, status)) ok = false;
                 const int c0 = sl * slab, cols = min(slab, K - c0);
@@ -439,23 +481,27 @@ skinny_stream_kernel(const SkinnyArgs a, int nstages, int slab_cols, int* status
                 if (ok) {
                     for (int blk = warp; blk < nblk; blk += kSkinnyWarps) {       // warp-uniform
                         const bool live = blk * 64 + t4 * 16 < cols;
-                        uint4 wa0 = make_uint4(0u, 0u, 0u, 0u), wa1 = wa0, wb0 = wa0, wb1 = wa0, xa = wa0, xb = wa0;
+                        uint4 wa0 = make_uint4(0u, 0u, 0u, 0u), wa1 = wa0, wb0 = wa0, wb1 = wa0;
                         if (live) {
                             const uint4* pa = reinterpret_cast<const uint4*>(st + size_t(g) * rowb + (blk * 64 + t4 * 16) * 2);
                             const uint4* pb = reinterpret_cast<const uint4*>(st + size_t(g + 8) * rowb + (blk * 64 + t4 * 16) * 2);
                             wa0 = pa[0]; wa1 = pa[1]; wb0 = pb[0]; wb1 = pb[1];
-                            if (g < Mp) {
-                                const uint4* xp = reinterpret_cast<const uint4*>(xrow + c0 + blk * 64);
-                                xa = xp[0]; xb = xp[1];
-                            }
                         }
                         const uint32_t wA[8] = {wa0.x, wa0.y, wa0.z, wa0.w, wa1.x, wa1.y, wa1.z, wa1.w};
                         const uint32_t wB[8] = {wb0.x, wb0.y, wb0.z, wb0.w, wb1.x, wb1.y, wb1.z, wb1.w};
-                        const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
                         #pragma unroll
-                        for (int s = 0; s < 4; ++s) {
-                            const uint32_t af[4] = {wA[2 * s], wB[2 * s], wA[2 * s + 1], wB[2 * s + 1]};
-                            mma_16816<T>(acc, af, xw[2 * s], xw[2 * s + 1]);
+                        for (int mh = 0; mh < MH; ++mh) {
+                            uint4 xa = make_uint4(0u, 0u, 0u, 0u), xb = xa;
+                            if (live && g + 8 * mh < Mp) {
+                                const uint4* xp = reinterpret_cast<const uint4*>(xrow + size_t(8 * mh) * xstride + c0 + blk * 64);
+                                xa = xp[0]; xb = xp[1];
+                            }
+                            const uint32_t xw[8] = {xa.x, xa.y, xa.z, xa.w, xb.x, xb.y, xb.z, xb.w};
+                            #pragma unroll
+                            for (int s = 0; s < 4; ++s) {
+                                const uint32_t af[4] = {wA[2 * s], wB[2 * s], wA[2 * s + 1], wB[2 * s + 1]};
+                                mma_16816<T>(acc[mh], af, xw[2 * s], xw[2 * s + 1]);
+                            }
                         }
                     }
                 }
@@ -463,9 +509,11 @@ skinny_stream_kernel(const SkinnyArgs a, int nstages, int slab_cols, int* status
                 if (lane == 0) dme::mbar_arrive(&empty_bar[stage]);
                 if (++stage == nstages) { stage = 0; phase ^= 1u; }
             }
-            *reinterpret_cast<float4*>(&red[parity][warp][lane][0]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+            #pragma unroll
+            for (int mh = 0; mh < MH; ++mh)
+                *reinterpret_cast<float4*>(&red[parity][warp][lane][4 * mh]) = make_float4(acc[mh][0], acc[mh][1], acc[mh][2], acc[mh][3]);
             skinny_barrier();
-            skinny_epilogue<T, EPI, 2>(a, red[parity], grp, threadIdx.x, false, 0.f);
+            skinny_epilogue<T, EPI, 2, MH>(a, red[parity], grp, threadIdx.x, false, 0.f);
         }
         if (!ok && lane == 0) atomicExch(sticky, 1);
     }
@@ -474,15 +522,24 @@ skinny_stream_kernel(const SkinnyArgs a, int nstages, int slab_cols, int* status
 // Launch: returns B200P_E_RANGE when the shape is outside the kernel's domain (the caller then
 // takes the library GEMM).  K must be a multiple of 16 (32-byte steps along the rows of W and X),
 // ldx of 8, W 32-byte aligned.
+template <typename T, int PRO, int EPI, int MH>
+int launch_skinny_mh(const SkinnyArgs& a, cudaStream_t st);
+
+// Up to 8 rows of X: one B fragment per A fragment; 9 .. 16 rows: two.
 template <typename T, int PRO, int EPI>
 int launch_skinny(const SkinnyArgs& a, cudaStream_t st) {
+    return a.M <= 8 ? launch_skinny_mh<T, PRO, EPI, 1>(a, st) : launch_skinny_mh<T, PRO, EPI, 2>(a, st);
+}
+
+template <typename T, int PRO, int EPI, int MH>
+int launch_skinny_mh(const SkinnyArgs& a, cudaStream_t st) {
     if (a.M < 1 || a.M > kSkinnyMaxM || a.K < 16 || a.K % 16 != 0 || a.N < 1) return B200P_E_RANGE;
     if (PRO == PRO_PLAIN && (a.ldx % 8 != 0 || !aligned(a.X16, 16))) return B200P_E_RANGE;
     if (PRO == PRO_RMSNORM && (!aligned(a.X32, 16) || !aligned(a.norm_w, 8))) return B200P_E_RANGE;
     if (!aligned(a.W, 16)) return B200P_E_RANGE;               // bulk copies need 16 bytes; the register kernel's 32-byte loads are checked below
-    const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : 8;
+    const int Mp = a.M <= 1 ? 1 : a.M <= 2 ? 2 : a.M <= 4 ? 4 : a.M <= 8 ? 8 : 16;
     const size_t smem = size_t(Mp) * (a.K + kSkinnyXPad) * 2;
-    if (smem > 200 * 1024) return B200P_E_RANGE;
+    if (smem > 190 * 1024) return B200P_E_RANGE;
     if (EPI == EPI_ROPE && (a.rope.D % 16 != 0 || a.N != (a.rope.nQH + 2 * a.rope.nKVH) * a.rope.D)) return B200P_E_RANGE;
     const int sms = sm_count() > 0 ? sm_count() : 148;
     constexpr bool paired = EPI == EPI_SILU16 || EPI == EPI_ROPE;
@@ -493,7 +550,7 @@ int launch_skinny(const SkinnyArgs& a, cudaStream_t st) {
         const int slab = a.K < slab_cols ? a.K : slab_cols;
         const int stage_bytes = 16 * (slab * 2 + 16);
         const int x_bytes = int((smem + 127) / 128 * 128);
-        int nstages = (224000 - x_bytes) / stage_bytes;
+        int nstages = (224000 - 8192 * (MH - 1) - x_bytes) / stage_bytes;
         if (nstages > 8) nstages = 8;
         int* sticky = device_status_ptr();
         int* status = a.abort_word;
@@ -505,7 +562,7 @@ int launch_skinny(const SkinnyArgs& a, cudaStream_t st) {
         if (nstages >= 2 && sticky) {
             const int groups = EPI == EPI_SILU16 ? (a.N + 7) / 8 : (a.N + 15) / 16;
             const size_t dyn = size_t(x_bytes) + size_t(nstages) * stage_bytes;
-            void (*sk)(SkinnyArgs, int, int, int*, int*) = skinny_stream_kernel<T, PRO, EPI>;
+            void (*sk)(SkinnyArgs, int, int, int*, int*) = skinny_stream_kernel<T, PRO, EPI, MH>;
             const cudaError_t ae = cudaFuncSetAttribute(sk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn));
             if (ae != cudaSuccess) return int(ae);
             cudaLaunchConfig_t cfg{};
@@ -524,9 +581,9 @@ int launch_skinny(const SkinnyArgs& a, cudaStream_t st) {
     const bool half_rows = !paired && (a.N + 15) / 16 < (4 * sms) / 3;
     const int ngroups = EPI == EPI_SILU16 ? (a.N + 7) / 8 : half_rows ? (a.N + 7) / 8 : (a.N + 15) / 16;
     const int grid = ngroups < 2 * sms ? ngroups : 2 * sms;      // CTAs loop over their groups, loads running ahead
-    void (*kern)(SkinnyArgs) = skinny_gemm_kernel<T, PRO, EPI, 2>;
-    if constexpr (!paired) { if (half_rows) kern = skinny_gemm_kernel<T, PRO, EPI, 1>; }
-    if (smem > 36 * 1024) {                                     // static (8 KB) + dynamic beyond 48 KB needs the opt-in
+    void (*kern)(SkinnyArgs) = skinny_gemm_kernel<T, PRO, EPI, 2, MH>;
+    if constexpr (!paired) { if (half_rows) kern = skinny_gemm_kernel<T, PRO, EPI, 1, MH>; }
+    if (smem > 28 * 1024) {                                     // static (8 or 16 KB) + dynamic beyond 48 KB needs the opt-in
         const cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, int(smem));
         if (e != cudaSuccess) return int(e);
     }

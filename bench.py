@@ -372,6 +372,33 @@ class PrefillCausal:
 
     e2e_note = "host-buffer prefill (hostpipe.prefill_host): one chunk per sequence, H2D / kernel / D2H on three streams"
 
+    def extra_fields(self):
+        """The same kernel off the headline shape (device-resident, 10 launches each after 3 warm-ups): non-causal,
+        twice the sequence length, and head dimension 64 (the runtime's shape)."""
+        torch, pkg = self.torch, self.pkg
+        out = {}
+        for label, (B, H, S, D, causal) in (("non_causal_s4096_d128", (8, 32, 4096, 128, False)),
+                                             ("causal_s8192_d128", (4, 32, 8192, 128, True)),
+                                             ("causal_s4096_d64", (8, 32, 4096, 64, True)),
+                                             ("causal_s512_d64_gqa_32q_4kv", (16, 32, 512, 64, True))):
+            g = torch.Generator(device=self.Q.device); g.manual_seed(0xB203 + S + D)
+            hkv = 4 if "gqa" in label else H
+            q = (torch.randn(B, H, S, D, device=self.Q.device, generator=g) * 0.5).bfloat16()
+            k = (torch.randn(B, hkv, S, D, device=self.Q.device, generator=g) * 0.5).bfloat16()
+            v = (torch.randn(B, hkv, S, D, device=self.Q.device, generator=g) * 0.5).bfloat16()
+            o = torch.empty_like(q)
+            for _ in range(3):
+                pkg.prefill(q, k, v, causal=causal, out=o)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(10):
+                pkg.prefill(q, k, v, causal=causal, out=o)
+            b.record(); b.synchronize()
+            ms = a.elapsed_time(b) / 10
+            out[label] = {"ms": round(ms, 4), "TFLOP/s": round(4.0 * B * H * S * S * D * (0.5 if causal else 1.0) / ms / 1e9, 1)}
+            del q, k, v, o
+        return {"other_shapes": out}
+
     def cpu_run(self, orc, n, threads, reps=1):
         """n = (batch, head) units at full sequence length."""
         import numpy as np

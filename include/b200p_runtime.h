@@ -99,7 +99,7 @@ int b200p_session_prefill_logits(b200p_session* s, const int* input_ids, int T, 
  * feeds token_ids [batch] (host) at position kv_len, returns logits [batch, vocab]. */
 int b200p_session_step_logits(b200p_session* s, const int* token_ids, float* logits, b200p_stream_t stream);
 
-/* The decode step's projection kernel on its own: Y[M, N] = X[M, K] . W[N, K]^T for M <= 8,
+/* The decode step's projection kernel on its own: Y[M, N] = X[M, K] . W[N, K]^T for M <= 16,
  * 16-bit operands, fp32 accumulation.  Stands in for the rocBLAS calls of the decode step
  * (rocblas_gemm.hpp:112-209) together with the kernels around them:
  *   prologue 0: X = x16 [M, ldx] (16-bit);

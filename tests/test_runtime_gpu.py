@@ -58,11 +58,13 @@ def test_prefill_and_teacher_forced_decode(b200p, torch_cuda, cfg, kind, bias, T
     sess.close()
 
 
-def test_generate_equals_stepwise_greedy(b200p, torch_cuda):
+@pytest.mark.parametrize("batch", [3, 12])
+def test_generate_equals_stepwise_greedy(b200p, torch_cuda, batch):
     """generate() keeps the next-token ids on the device; it must produce exactly the tokens
-    of the host-driven loop over prefill_logits / step_logits on the same session."""
+    of the host-driven loop over prefill_logits / step_logits on the same session.  Twelve
+    sequences put the decode step on the projection kernels' two-fragment (9 .. 16 row) forms."""
     torch = torch_cuda
-    cfg, kind, batch, max_seq, T, new = SMALL, "bf16", 3, 128, 40, 12
+    cfg, kind, max_seq, T, new = SMALL, "bf16", 128, 40, 12
     w = rr.make_weights(cfg, seed=3, kind=kind, std=0.05)
     dw = to_device(torch, w, kind)
     sess = b200p.Session(cfg, dw, max_seq, batch)
@@ -86,6 +88,11 @@ def test_generate_equals_stepwise_greedy(b200p, torch_cuda):
     srt = np.sort(orc.round_to(r, kind), axis=-1)
     clear = (srt[:, -1] - srt[:, -2]) > 0.1 * r.std()
     assert (toks[clear, 0] == ref.argmax(r)[clear]).all()
+    # and every decode step's logits against the oracle, teacher-forced on this library's tokens
+    lg = sess.prefill_logits(ids)
+    for s in range(3):
+        g, r = sess.step_logits(toks[:, s].copy()), ref.step_logits(toks[:, s].copy())
+        check_logits(g, r)
     sess.close()
 
 

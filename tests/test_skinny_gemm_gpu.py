@@ -29,7 +29,10 @@ def rmsnorm16(x, w, kind, eps=1e-6):
     return orc.round_to((x * inv * w).astype(np.float32), kind).astype(np.float64)
 
 
-SHAPES = [(1, 96, 64), (2, 2560, 2048), (3, 130, 528), (4, 2048, 5632), (8, 77, 1040), (5, 33, 16)]
+# 9 .. 16 rows take the two-fragment kernels; (16, 2048, 5632) does not fit the staged kernel's shared memory
+# beside X and goes to the register kernel whatever the knob says
+SHAPES = [(1, 96, 64), (2, 2560, 2048), (3, 130, 528), (4, 2048, 5632), (8, 77, 1040), (5, 33, 16),
+          (9, 130, 528), (12, 2560, 2048), (16, 2048, 5632), (16, 77, 1040), (13, 33, 16)]
 
 
 @pytest.mark.parametrize("kind", ["bf16", "f16"])
@@ -76,7 +79,7 @@ def test_plain_prologue_residual_epilogue(b200p, torch_cuda, kind, M, N, K):
 
 
 @pytest.mark.parametrize("kind", ["bf16", "f16"])
-@pytest.mark.parametrize("M,F,K", [(2, 5632, 2048), (1, 40, 64), (8, 300, 512)])
+@pytest.mark.parametrize("M,F,K", [(2, 5632, 2048), (1, 40, 64), (8, 300, 512), (11, 300, 512), (16, 5632, 2048)])
 def test_silu_epilogue(b200p, torch_cuda, kind, M, F, K):
     torch = torch_cuda
     rng = np.random.default_rng(F)
@@ -101,8 +104,8 @@ def test_shapes_outside_the_domain_are_refused(b200p, torch_cuda):
     with pytest.raises(b200p.B200PError):
         b200p.skinny_gemm(W, out, x16=X, epilogue="acc32")
     W = torch.zeros((64, 32), dtype=torch.bfloat16, device="cuda")
-    X = torch.zeros((9, 32), dtype=torch.bfloat16, device="cuda")           # more than 8 rows
-    out = torch.zeros((9, 64), dtype=torch.float32, device="cuda")
+    X = torch.zeros((17, 32), dtype=torch.bfloat16, device="cuda")          # more than 16 rows
+    out = torch.zeros((17, 64), dtype=torch.float32, device="cuda")
     with pytest.raises(b200p.B200PError):
         b200p.skinny_gemm(W, out, x16=X, epilogue="acc32")
     with pytest.raises(b200p.B200PError):
