@@ -67,6 +67,7 @@ SYMBOLS = {
     "b200p_session_blas_calls": (C.c_ulonglong, [_vp]),
     "b200p_gemm_16": (_i, [_i, _i, _vp, _vp, _vp, _i, _i, _i, _ll, _ll, _ll, _vp]),
     "b200p_session_graph_replays": (C.c_ulonglong, [_vp]),
+    "b200p_session_mega_launches": (C.c_ulonglong, [_vp]),
     "b200p_fa_step": (_i, [_i, _i, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, C.c_float, _vp]),
 }
 
@@ -660,3 +661,8 @@ class Session:
     @property
     def graph_replays(self) -> int:
         return int(lib().b200p_session_graph_replays(self._h))
+
+    @property
+    def mega_launches(self) -> int:
+        """Launches of the persistent decode kernel (all decode steps of a generate() call in one)."""
+        return int(lib().b200p_session_mega_launches(self._h))

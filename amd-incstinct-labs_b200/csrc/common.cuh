@@ -33,6 +33,8 @@ enum Knob {
     KNOB_SCAN16_LANE,           // 1: 16-bit scans hold a whole segment per lane, 0: four lanes per segment
     KNOB_RUNTIME_GEMM,          // prefill projections: 1 the tcgen05 GEMM of this library (default), 0 library GEMMs
     KNOB_GEMM_TILE_N,           // 128 or 256: force the tensor-core GEMM's tile width (0: chosen from the shape)
+    KNOB_RUNTIME_MEGA,          // 1: the greedy loop's decode steps run as one persistent cooperative kernel, 0: kernel per phase (default)
+    KNOB_RUNTIME_MEGA_AHEAD,    // persistent decode kernel: stages of L2 prefetch in front of the shared-memory ring's loads
     KNOB_COUNT
 };
 

@@ -16,6 +16,7 @@ struct KnobInit { KnobInit() { for (auto& k : g_knobs) k.store(-1); } } g_knob_i
 const char* const kKnobNames[KNOB_COUNT] = {
     "seg_vec_bytes", "seg_ctas_per_sm", "scan_fp_exact", "decode_splits", "decode_fused_combine", "decode_variant", "prefill_variant",
     "runtime_graph", "runtime_pdl", "runtime_rope_fused", "runtime_skinny", "scan16_lane", "runtime_gemm", "gemm_tile_n",
+    "runtime_mega", "runtime_mega_ahead",
 };
 constexpr int kMaxDevices = 64;
 std::atomic<int> g_sms[kMaxDevices];

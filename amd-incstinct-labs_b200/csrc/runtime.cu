@@ -27,6 +27,7 @@
 #include "attn_common.cuh"
 #include "wave_primitives/wave64.cuh"
 #include "skinny_gemm.cuh"
+#include "decode_mega.cuh"
 #include "status_rc.hpp"
 #include "gemm_tc.cuh"
 #include "b200p_runtime.h"
@@ -230,6 +231,11 @@ struct b200p_session {
     const void* graph_hidden = nullptr; const int* graph_tokens = nullptr; int graph_max_new = 0; unsigned graph_epoch = 0;
     unsigned long long graph_replays = 0, graph_kernels = 0;   // kernels of this library inside one replay
     unsigned long long gemm_calls = 0, blas_calls = 0;      // all projections / those that went to the GEMM library
+    // the decode loop as one persistent kernel (decode_mega.cuh): per-layer pointer table, split scratch, counters
+    MegaLayer* mega_layers = nullptr;
+    float* mega_part = nullptr;
+    unsigned* mega_words = nullptr;                      // [0] grid barrier, [1] key readers
+    unsigned long long mega_launches = 0;
     std::vector<void*> owned;
 
     template <typename P> cudaError_t alloc(P** p, size_t bytes) {
@@ -473,6 +479,88 @@ int embed(b200p_session* s, int M, cudaStream_t st) {
     return launched();
 }
 
+// ---- the decode loop as one persistent kernel (decode_mega.cuh) ---------------------------------------
+struct MegaPlan { const void* kernel = nullptr; int nstages = 0, x_bytes = 0, tab_bytes = 0, stage_bytes = 0; size_t dyn = 0; };
+
+template <typename T>
+const void* mega_kernel(int D) {
+    return D == 64 ? reinterpret_cast<const void*>(decode_mega_kernel<T, 2>) : D == 128 ? reinterpret_cast<const void*>(decode_mega_kernel<T, 4>) : nullptr;
+}
+
+// Whether (and how) this session's decode steps run as the persistent kernel: the projection kernels' domain,
+// at most 8 sequences, heads of 64 or 128 columns, a device that launches
+// cooperatively, and room for at least two weight stages beside X.
+template <typename T>
+bool mega_plan(const b200p_session* s, MegaPlan* out) {
+    const auto& c = s->c;
+    if (tuning(KNOB_RUNTIME_MEGA, 0) == 0 || tuning(KNOB_RUNTIME_SKINNY, 2) != 2 || !s->mega_layers) return false;
+    if (!skinny_ok(s, s->batch) || s->batch > kMegaMaxRows || c.n_kv_heads < 1 || c.n_heads % c.n_kv_heads != 0) return false;
+    const int D = c.head_dim;
+    MegaPlan pl;
+    pl.kernel = mega_kernel<T>(D);
+    if (!pl.kernel || device_status_ptr() == nullptr) return false;
+    const int B = s->batch, Mp = B <= 1 ? 1 : B <= 2 ? 2 : B <= 4 ? 4 : 8;
+    const int maxK = std::max(std::max(c.hidden, c.ffn_dim), s->qd);
+    const int slab = std::min(kSkinnySlab, maxK);
+    const size_t x_need = size_t(Mp) * (maxK + kSkinnyXPad) * 2;
+    const size_t att_need = size_t(kSkinnyWarps) * (2 * D + 2) * sizeof(float);
+    pl.x_bytes = int((std::max(x_need, att_need) + 127) / 128 * 128);
+    pl.stage_bytes = 16 * (slab * 2 + 16);
+    const int budget = 232448 - 8704;                          // shared memory per CTA minus the kernel's static part
+    pl.tab_bytes = int((size_t(c.n_layers) * sizeof(MegaLayer) + 127) / 128 * 128);
+    pl.nstages = std::min(kSkinnyMaxStages, (budget - pl.x_bytes - pl.tab_bytes) / pl.stage_bytes);
+    if (pl.nstages < 2) return false;
+    pl.dyn = size_t(pl.x_bytes) + pl.tab_bytes + size_t(pl.nstages) * pl.stage_bytes;
+    int dev = 0, coop = 0, per_sm = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess || !coop) {
+        cudaGetLastError();
+        return false;
+    }
+    if (cudaFuncSetAttribute(pl.kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, int(pl.dyn)) != cudaSuccess ||
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, pl.kernel, kSkinnyStreamThreads, pl.dyn) != cudaSuccess || per_sm < 1) {
+        cudaGetLastError();
+        return false;
+    }
+    *out = pl;
+    return true;
+}
+
+// n_steps decode steps from the device-side state (position, output column) and the ids in ids_in.
+template <typename T>
+int mega_launch(b200p_session* s, const MegaPlan& pl, const int* ids_in, int n_steps, bool want_argmax, int* tokens, int tokens_stride,
+                cudaStream_t st) {
+    const auto& c = s->c;
+    if (cudaError_t e = cudaMemsetAsync(s->mega_words, 0, sizeof(unsigned), st)) return int(e);      // the grid barrier's counter
+    MegaParams p{};
+    p.layers = s->mega_layers; p.n_layers = c.n_layers; p.B = s->batch; p.H = c.hidden; p.F = c.ffn_dim; p.D = c.head_dim;
+    p.nQH = c.n_heads; p.nKVH = c.n_kv_heads; p.V = c.vocab_size; p.max_seq = s->max_seq;
+    p.embed = s->embed; p.lm_head = s->lm_head; p.final_norm = s->final_norm;
+    p.hidden = s->hidden; p.qkv = s->qkv; p.act = s->act; p.logits = s->logits;
+    p.kcache = s->kcache; p.vcache = s->vcache; p.layer_cache_elems = s->layer_cache_elems();
+    p.cos_t = s->cos_t; p.sin_t = s->sin_t;
+    p.part = s->mega_part;
+    p.ids_in = ids_in; p.next_ids = s->d_next; p.tokens = tokens; p.tokens_stride = tokens_stride; p.state = s->d_state;
+    p.keys = s->d_keys; p.key_ticket = s->mega_words + 1; p.bar = s->mega_words;
+    p.status = s->d_abort; p.sticky = device_status_ptr();
+    p.n_steps = n_steps; p.want_argmax = want_argmax ? 1 : 0;
+    p.nstages = pl.nstages; p.slab_cols = kSkinnySlab; p.x_bytes = pl.x_bytes; p.tab_bytes = pl.tab_bytes; p.stage_bytes = pl.stage_bytes;
+    p.ahead = tuning(KNOB_RUNTIME_MEGA_AHEAD, 4);
+    p.eps = 1e-6f; p.scale_log2 = (1.f / sqrtf(float(c.head_dim))) * 1.4426950408889634f;
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(unsigned(sm_count())); cfg.blockDim = dim3(kSkinnyStreamThreads); cfg.dynamicSmemBytes = pl.dyn; cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeCooperative;
+    attr[0].val.cooperative = 1;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    void* args[] = {&p};
+    const cudaError_t le = cudaLaunchKernelExC(&cfg, pl.kernel, args);
+    if (le != cudaSuccess) { cudaGetLastError(); return int(le); }
+    g_launches.fetch_add(1, std::memory_order_relaxed);
+    ++s->mega_launches;
+    s->gemm_calls += (unsigned long long)(n_steps) * (4ull * c.n_layers + 1);
+    return B200P_OK;
+}
+
 // One greedy decode step with every per-step quantity read on the device: embed the ids the
 // previous argmax left in d_next, run the layers at position state[0], argmax into column
 // state[1] of the token table, advance the state.  Launch parameters never change, so the
@@ -559,7 +647,15 @@ int generate(b200p_session* s, const int* ids, int Tn, int max_new, int* out, fl
         set_state_kernel<<<1, 1, 0, st>>>(s->d_state, Tn, 1);
         launched(2);
         cudaEventRecord(e1, st);
-        for (int step = 1; step < max_new; ++step) {
+        MegaPlan mega;
+        const bool use_mega = max_new > 1 && mega_plan<T>(s, &mega);
+        if (use_mega) {
+            // all remaining steps in one launch: the ids, the position and the output column stay on the device
+            if (Tn + max_new - 2 >= s->max_seq) { rc = B200P_E_RANGE; break; }
+            if ((rc = mega_launch<T>(s, mega, s->d_next, max_new - 1, true, s->d_tokens, max_new, st))) break;
+            s->kv_len += max_new - 1;
+        }
+        for (int step = 1; step < max_new && !use_mega; ++step) {
             if (s->kv_len >= s->max_seq) { rc = B200P_E_RANGE; break; }
             if (use_graph && step >= 2) {
                 // the first decode step ran eagerly below; from the second on, replay the captured step
@@ -617,13 +713,20 @@ int step_logits(b200p_session* s, const int* ids, float* logits, cudaStream_t st
     const int B = s->batch;
     if (int e = clear_status(s, st)) return e;
     if (cudaError_t e = cudaMemcpyAsync(s->d_ids, ids, size_t(B) * sizeof(int), cudaMemcpyHostToDevice, st)) return int(e);
-    if (int e = embed<T>(s, B, st)) return e;
     // same device-side position and split plan as the greedy loop, so that both give the same bits
     set_state_kernel<<<1, 1, 0, st>>>(s->d_state, s->kv_len, 0);
     launched();
-    if (int e = run_layers<T>(s, 1, 0, st, s->d_state)) return e;
-    s->kv_len += 1;
-    if (int e = skinny_ok(s, B) ? last_logits_skinny<T>(s, st) : last_logits<T>(s, 1, st)) return e;
+    MegaPlan mega;
+    if (mega_plan<T>(s, &mega)) {
+        // the greedy loop's kernel for one step, logits only: same arithmetic, so both give the same bits
+        if (int e = mega_launch<T>(s, mega, s->d_ids, 1, false, nullptr, 0, st)) return e;
+        s->kv_len += 1;
+    } else {
+        if (int e = embed<T>(s, B, st)) return e;
+        if (int e = run_layers<T>(s, 1, 0, st, s->d_state)) return e;
+        s->kv_len += 1;
+        if (int e = skinny_ok(s, B) ? last_logits_skinny<T>(s, st) : last_logits<T>(s, 1, st)) return e;
+    }
     if (cudaError_t e = cudaMemcpyAsync(logits, s->logits, size_t(B) * s->c.vocab_size * 4, cudaMemcpyDeviceToHost, st)) return int(e);
     int words[2] = {0, 0};
     if (int e = fetch_status(s, words, st)) return e;
@@ -686,6 +789,20 @@ int build(b200p_session* s, const b200p_model_weights* w) {
     if ((e = cudaMemset(s->d_keys, 0, size_t(s->batch) * sizeof(unsigned long long)))) return int(e);
     if ((e = cudaMemset(s->d_tickets, 0, size_t(s->batch) * sizeof(unsigned int)))) return int(e);
     if ((e = s->alloc(&s->blas_ws, b200p_session::kBlasWsBytes))) return int(e);
+    // the persistent decode kernel's tables and scratch (decode_mega.cuh), when the shape is in its domain
+    if (s->batch <= kMegaMaxRows && c.n_heads / c.n_kv_heads <= kMegaMaxGroup) {
+        std::vector<MegaLayer> ml(c.n_layers);
+        for (int li = 0; li < c.n_layers; ++li) {
+            const b200p_layer_weights& L = s->layers[li];
+            ml[li] = MegaLayer{s->Wqkv[li], s->bqkv[li], L.Wo, s->Wgu[li], L.Wdown, L.norm_attn, L.norm_mlp};
+        }
+        const size_t units = size_t(s->batch) * c.n_heads;
+        if ((e = s->alloc(&s->mega_layers, ml.size() * sizeof(MegaLayer)))) return int(e);
+        if ((e = cudaMemcpy(s->mega_layers, ml.data(), ml.size() * sizeof(MegaLayer), cudaMemcpyHostToDevice))) return int(e);
+        if ((e = s->alloc(&s->mega_part, units * kMegaMaxSplits * kMegaPartPad(D) * sizeof(float)))) return int(e);
+        if ((e = s->alloc(&s->mega_words, 2 * sizeof(unsigned)))) return int(e);
+        if ((e = cudaMemset(s->mega_words, 0, 2 * sizeof(unsigned)))) return int(e);
+    }
     // decode scratch for the longest cache
     b200p_decode_args a{};
     a.D = D; a.N = s->max_seq; a.nQHeads = c.n_heads; a.nKVHeads = c.n_kv_heads; a.stride_kv = s->max_seq; a.batch = s->batch; a.dtype = s->dtype;
@@ -791,3 +908,4 @@ extern "C" int b200p_session_kv_len(const b200p_session* s) { return s ? s->kv_l
 extern "C" unsigned long long b200p_session_gemm_calls(const b200p_session* s) { return s ? s->gemm_calls : 0; }
 extern "C" unsigned long long b200p_session_blas_calls(const b200p_session* s) { return s ? s->blas_calls : 0; }
 extern "C" unsigned long long b200p_session_graph_replays(const b200p_session* s) { return s ? s->graph_replays : 0; }
+extern "C" unsigned long long b200p_session_mega_launches(const b200p_session* s) { return s ? s->mega_launches : 0; }

@@ -56,7 +56,8 @@
 namespace b200p {
 
 enum SkinnyPrologue { PRO_PLAIN = 0, PRO_RMSNORM = 1 };
-enum SkinnyEpilogue { EPI_STORE16 = 0, EPI_ACC32 = 1, EPI_STORE32 = 2, EPI_SILU16 = 3, EPI_ROPE = 4 };
+enum SkinnyEpilogue { EPI_STORE16 = 0, EPI_ACC32 = 1, EPI_STORE32 = 2, EPI_SILU16 = 3, EPI_ROPE = 4,
+                      EPI_STORE32_BEST = 5 };   // fp32 store + running argmax key per row (decode_mega.cuh only)
 
 // EPI_ROPE: W is the concatenated Q/K/V projection; the epilogue is the reference's bias add,
 // rotate-half RoPE and KV-cache scatter (forward.hpp:135-148, 211-224; rocblas_gemm.hpp:56-63)
@@ -77,6 +78,8 @@ struct SkinnyArgs {
     const void*  X16;      // PRO_PLAIN:   [M][ldx] 16-bit activations
     const float* X32;      // PRO_RMSNORM: [M][K] fp32 residual stream
     const void*  norm_w;   // PRO_RMSNORM: [K] 16-bit norm weights
+    const void*  Xemb;     // skinny_prologue<T, PRO_RMSNORM, true>: row m of X is float(Xemb[Xids[m]][:]) (16-bit table [*][K]) instead of X32
+    const int*   Xids;
     void*        out;      // [M][ldo] 16-bit or fp32
     int M, N, K, ldx, ldo;
     float eps;
@@ -97,7 +100,7 @@ constexpr int kSkinnyXPad = 8;        // elements: X rows are 16 bytes longer th
 __device__ __forceinline__ void skinny_barrier() { asm volatile("bar.sync 1, %0;" :: "r"(kSkinnyThreads) : "memory"); }
 
 // X into shared memory as 16-bit rows of K + kSkinnyXPad elements, rows in [M, Mp) zero; ends with a barrier.
-template <typename T, int PRO>
+template <typename T, int PRO, bool EMB = false>
 __device__ __forceinline__ void skinny_prologue(const SkinnyArgs& a, T* xs, float* part_ss, int Mp, int warp, int lane) {
     const int K = a.K, xstride = K + kSkinnyXPad;
     // ---- prologue: X into shared memory as 16-bit, rows in [M, Mp) zero --------------------------------
@@ -137,6 +140,13 @@ __device__ __forceinline__ void skinny_prologue(const SkinnyArgs& a, T* xs, floa
         const int quads = K / 4, qper = (quads + wpr - 1) / wpr;
         const int q0 = part * qper, q1 = min(q0 + qper, quads);
         const float* x = a.X32 + size_t(m) * K;
+        const T* xe = EMB && m < a.M ? static_cast<const T*>(a.Xemb) + size_t(a.Xids[m]) * K : nullptr;
+        auto ldx = [&](int q) -> float4 {                       // four elements of row m as fp32
+            if (!EMB) return *reinterpret_cast<const float4*>(x + 4 * q);
+            const uint2 r = *reinterpret_cast<const uint2*>(xe + 4 * q);
+            const T* e = reinterpret_cast<const T*>(&r);
+            return make_float4(to_float(e[0]), to_float(e[1]), to_float(e[2]), to_float(e[3]));
+        };
         const T* nw = static_cast<const T*>(a.norm_w);
         T* dst = xs + size_t(m) * xstride;
         float4 cx[CACHE]; uint2 cw[CACHE];
@@ -146,13 +156,13 @@ __device__ __forceinline__ void skinny_prologue(const SkinnyArgs& a, T* xs, floa
             for (int it = 0; it < CACHE; ++it) {
                 const int q = q0 + lane + 32 * it;
                 if (q < q1) {
-                    cx[it] = *reinterpret_cast<const float4*>(x + 4 * q);
+                    cx[it] = ldx(q);
                     cw[it] = *reinterpret_cast<const uint2*>(nw + 4 * q);
                     ss += cx[it].x * cx[it].x + cx[it].y * cx[it].y + cx[it].z * cx[it].z + cx[it].w * cx[it].w;
                 }
             }
             for (int q = q0 + lane + 32 * CACHE; q < q1; q += 32) {
-                const float4 v = *reinterpret_cast<const float4*>(x + 4 * q);
+                const float4 v = ldx(q);
                 ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
             }
         }
@@ -176,7 +186,7 @@ __device__ __forceinline__ void skinny_prologue(const SkinnyArgs& a, T* xs, floa
                 if (q < q1) put(q, cx[it], cw[it]);
             }
             for (int q = q0 + lane + 32 * CACHE; q < q1; q += 32)
-                put(q, *reinterpret_cast<const float4*>(x + 4 * q), *reinterpret_cast<const uint2*>(nw + 4 * q));
+                put(q, ldx(q), *reinterpret_cast<const uint2*>(nw + 4 * q));
         } else {
             for (int q = q0 + lane; q < q1; q += 32) *reinterpret_cast<uint2*>(dst + 4 * q) = make_uint2(0u, 0u);
         }
@@ -195,9 +205,48 @@ __device__ __forceinline__ void skinny_prologue(const SkinnyArgs& a, T* xs, floa
 
 // The eight warps' partial accumulators (red[warp][lane][4]: the m16n8 C fragments) meet; the first 64 * R
 // threads write the group's outputs.  prev: for EPI_ACC32, the residual values fetched ahead (use_prev).
+// What a thread's epilogue of row group grp reads from global memory, fetched BEFORE the group's products so
+// that the latency lies under them: the residual values (EPI_ACC32), the rotation's cos / sin and the bias
+// pair (EPI_ROPE).  The values must not change between the fetch and the epilogue: true after the grid
+// dependency wait / the grid barrier that precedes the product, since each output element has one owner.
+template <int MH>
+struct EpiAhead {
+    float prev[MH];
+    float c, sn, b0, b1;
+};
+template <typename T, int EPI, int R, int MH>
+__device__ __forceinline__ void skinny_epilogue_fetch(const SkinnyArgs& a, int grp, int tid, EpiAhead<MH>& e) {
+    if (EPI == EPI_ACC32) {
+        if (tid < 64 * R) {
+            const int l = tid % 32, c = tid / 32;
+            const int n = grp * 8 * R + l / 4 + 8 * (c >> 1);
+            #pragma unroll
+            for (int mh = 0; mh < MH; ++mh) {
+                const int m = 8 * mh + 2 * (l % 4) + (c & 1);
+                e.prev[mh] = (m < a.M && n < a.N) ? static_cast<const float*>(a.out)[size_t(m) * a.ldo + n] : 0.f;
+            }
+        }
+    } else if (EPI == EPI_ROPE) {
+        if (tid < 64) {
+            const SkinnyRope& r = a.rope;
+            const int l = tid % 32;
+            const int cph = r.D / 16, half = r.D / 2;
+            const int slot = grp / cph, d = (grp % cph) * 8 + l / 4;
+            const int pos = r.pos_dev ? min(*r.pos_dev, r.max_seq - 1) : r.pos0;
+            e.c = r.cos_t[size_t(pos) * half + d]; e.sn = r.sin_t[size_t(pos) * half + d];
+            e.b0 = e.b1 = 0.f;
+            if (r.bias) {
+                const T* bias = static_cast<const T*>(r.bias);
+                e.b0 = to_float(bias[slot * r.D + d]); e.b1 = to_float(bias[slot * r.D + d + half]);
+            }
+        }
+    }
+}
+
 // red[warp][lane][4 * mh + c]: the m16n8 C fragment of the MMA over rows 8 mh .. 8 mh + 7 of X.
 template <typename T, int EPI, int R, int MH>
-__device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, const float (*red)[32][4 * MH], int grp, int tid, bool use_prev, float prev) {
+__device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, const float (*red)[32][4 * MH], int grp, int tid, bool use_prev, float prev,
+                                                unsigned long long* best = nullptr, const EpiAhead<MH>* ahead = nullptr) {
     #pragma unroll
     for (int mh = 0; mh < MH; ++mh) {
         if (EPI == EPI_SILU16) {
@@ -224,12 +273,12 @@ __device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, const float
                     x0 = to_float(from_float<T>(x0)); x1 = to_float(from_float<T>(x1));      // the projection's 16-bit output
                     if (r.bias) {
                         const T* bias = static_cast<const T*>(r.bias);
-                        x0 = to_float(from_float<T>(x0 + to_float(bias[slot * r.D + d])));
-                        x1 = to_float(from_float<T>(x1 + to_float(bias[slot * r.D + d + half])));
+                        x0 = to_float(from_float<T>(x0 + (ahead ? ahead->b0 : to_float(bias[slot * r.D + d]))));
+                        x1 = to_float(from_float<T>(x1 + (ahead ? ahead->b1 : to_float(bias[slot * r.D + d + half]))));
                     }
                     const int pos = r.pos_dev ? min(*r.pos_dev, r.max_seq - 1) : r.pos0;
                     if (slot < r.nQH + r.nKVH) {                  // q or k: rotate
-                        const float c = r.cos_t[size_t(pos) * half + d], sn = r.sin_t[size_t(pos) * half + d];
+                        const float c = ahead ? ahead->c : r.cos_t[size_t(pos) * half + d], sn = ahead ? ahead->sn : r.sin_t[size_t(pos) * half + d];
                         const float y0 = x0 * c - x1 * sn, y1 = x1 * c + x0 * sn;
                         x0 = y0; x1 = y1;
                     }
@@ -255,6 +304,16 @@ __device__ __forceinline__ void skinny_epilogue(const SkinnyArgs& a, const float
                 const size_t idx = size_t(m) * a.ldo + n;
                 if (EPI == EPI_STORE16)      static_cast<T*>(a.out)[idx] = from_float<T>(v);
                 else if (EPI == EPI_STORE32) static_cast<float*>(a.out)[idx] = v;
+                else if (EPI == EPI_STORE32_BEST) {
+                    // forward.hpp:244-262: argmax over the 16-bit logits, ties to the lowest index, as a 64-bit key
+                    // (order-preserving value bits, then the complemented index); best[mh] belongs to row m
+                    static_cast<float*>(a.out)[idx] = v;
+                    unsigned u = __float_as_uint(to_float(from_float<T>(v)));
+                    u = (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+                    const unsigned long long key = (unsigned long long)u << 32 | (0xffffffffu - unsigned(n));
+                    if (key > best[mh]) best[mh] = key;
+                }
+                else if (ahead)              static_cast<float*>(a.out)[idx] = ahead->prev[mh] + v;
                 else if (use_prev && mh == 0) static_cast<float*>(a.out)[idx] = prev + v;
                 else                         static_cast<float*>(a.out)[idx] += v;
             }
@@ -473,12 +532,56 @@ skinny_stream_kernel(const SkinnyArgs a, int nstages, int slab_cols, int* status
             float acc[MH][4];
             #pragma unroll
             for (int mh = 0; mh < MH; ++mh) { acc[mh][0] = acc[mh][1] = acc[mh][2] = acc[mh][3] = 0.f; }
+            EpiAhead<MH> ahead;
+            skinny_epilogue_fetch<T, EPI, 2, MH>(a, grp, threadIdx.x, ahead);
             for (int sl = 0; sl < nslab; ++sl) {
                 if (ok && !dme::wait(&full_bar[stage], phase, status)) ok = false;
                 const int c0 = sl * slab, cols = min(slab, K - c0);
                 const int nblk = (cols + 63) / 64;
                 const unsigned char* st = stages + size_t(stage) * stage_bytes;
-                if (ok) {
+                if (ok && cols % (64 * kSkinnyWarps) == 0) {
+                    // whole blocks for every warp (the usual stage): nb blocks each, taken BB at a time with every
+                    // shared-memory load of the batch issued before its first MMA
+                    constexpr int BB = 4 / MH;
+                    const int nb = cols / (64 * kSkinnyWarps);
+                    const unsigned char* wrow_a = st + size_t(g) * rowb + t4 * 32;
+                    const unsigned char* wrow_b = st + size_t(g + 8) * rowb + t4 * 32;
+                    for (int b0 = 0; b0 < nb; b0 += BB) {                         // warp-uniform
+                        uint4 wv[BB][4], xv[BB][MH][2];
+                        #pragma unroll
+                        for (int b = 0; b < BB; ++b) {
+                            const int blk = warp + kSkinnyWarps * min(b0 + b, nb - 1);
+                            const uint4* pa = reinterpret_cast<const uint4*>(wrow_a + blk * 128);
+                            const uint4* pb = reinterpret_cast<const uint4*>(wrow_b + blk * 128);
+                            wv[b][0] = pa[0]; wv[b][1] = pa[1]; wv[b][2] = pb[0]; wv[b][3] = pb[1];
+                            #pragma unroll
+                            for (int mh = 0; mh < MH; ++mh) {
+                                xv[b][mh][0] = xv[b][mh][1] = make_uint4(0u, 0u, 0u, 0u);
+                                if (g + 8 * mh < Mp) {
+                                    const uint4* xp = reinterpret_cast<const uint4*>(xrow + size_t(8 * mh) * xstride + c0 + blk * 64);
+                                    xv[b][mh][0] = xp[0]; xv[b][mh][1] = xp[1];
+                                }
+                            }
+                        }
+                        #pragma unroll
+                        for (int b = 0; b < BB; ++b) {
+                            if (b0 + b < nb) {
+                                const uint32_t wA[8] = {wv[b][0].x, wv[b][0].y, wv[b][0].z, wv[b][0].w, wv[b][1].x, wv[b][1].y, wv[b][1].z, wv[b][1].w};
+                                const uint32_t wB[8] = {wv[b][2].x, wv[b][2].y, wv[b][2].z, wv[b][2].w, wv[b][3].x, wv[b][3].y, wv[b][3].z, wv[b][3].w};
+                                #pragma unroll
+                                for (int mh = 0; mh < MH; ++mh) {
+                                    const uint32_t xw[8] = {xv[b][mh][0].x, xv[b][mh][0].y, xv[b][mh][0].z, xv[b][mh][0].w,
+                                                            xv[b][mh][1].x, xv[b][mh][1].y, xv[b][mh][1].z, xv[b][mh][1].w};
+                                    #pragma unroll
+                                    for (int s = 0; s < 4; ++s) {
+                                        const uint32_t af[4] = {wA[2 * s], wB[2 * s], wA[2 * s + 1], wB[2 * s + 1]};
+                                        mma_16816<T>(acc[mh], af, xw[2 * s], xw[2 * s + 1]);
+                                    }
+                                }
+                            }
+                        }
+                    }
+                } else if (ok) {
                     for (int blk = warp; blk < nblk; blk += kSkinnyWarps) {       // warp-uniform
                         const bool live = blk * 64 + t4 * 16 < cols;
                         uint4 wa0 = make_uint4(0u, 0u, 0u, 0u), wa1 = wa0, wb0 = wa0, wb1 = wa0;
@@ -513,7 +616,7 @@ skinny_stream_kernel(const SkinnyArgs a, int nstages, int slab_cols, int* status
             for (int mh = 0; mh < MH; ++mh)
                 *reinterpret_cast<float4*>(&red[parity][warp][lane][4 * mh]) = make_float4(acc[mh][0], acc[mh][1], acc[mh][2], acc[mh][3]);
             skinny_barrier();
-            skinny_epilogue<T, EPI, 2, MH>(a, red[parity], grp, threadIdx.x, false, 0.f);
+            skinny_epilogue<T, EPI, 2, MH>(a, red[parity], grp, threadIdx.x, false, 0.f, nullptr, &ahead);
         }
         if (!ok && lane == 0) atomicExch(sticky, 1);
     }

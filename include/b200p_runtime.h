@@ -131,8 +131,16 @@ int b200p_session_kv_len(const b200p_session* s);
 unsigned long long b200p_session_gemm_calls(const b200p_session* s);
 unsigned long long b200p_session_blas_calls(const b200p_session* s);
 /* Decode steps of b200p_session_generate that ran as replays of the captured step graph
- * (every step after the first of a call, unless b200p_set_tuning("runtime_graph", 0)). */
+ * (every step after the first of a call when the steps run kernel by kernel, unless
+ * b200p_set_tuning("runtime_graph", 0)). */
 unsigned long long b200p_session_graph_replays(const b200p_session* s);
+/* Launches of the persistent decode kernel.  After b200p_set_tuning("runtime_mega", 1),
+ * b200p_session_generate runs ALL the decode steps of a call as one cooperative launch (one CTA per
+ * SM, weights streamed through the phase boundaries, grid barriers with bounded waits between
+ * phases) and b200p_session_step_logits runs its step as one such launch, when the session has at
+ * most 8 sequences and the projection kernels' shapes.  Off by default: measured slower than the
+ * kernel-per-phase step replayed as a graph (session.hpp:263-331). */
+unsigned long long b200p_session_mega_launches(const b200p_session* s);
 
 #ifdef __cplusplus
 }

@@ -99,6 +99,11 @@ __device__ __forceinline__ void copy_tile_1d_stream(void* smem_dst, const void* 
                  :: "r"(smem_addr(smem_dst)), "l"(gmem_src), "r"(bytes), "r"(smem_addr(bar)), "l"(policy) : "memory");
 }
 
+// Hint: bring `bytes` (a multiple of 16, from a 16-byte aligned address) of global memory into L2; nothing to wait for.
+__device__ __forceinline__ void prefetch_l2(const void* gmem_src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" :: "l"(gmem_src), "r"(bytes) : "memory");
+}
+
 // Tiled tensor-map copies: box at element coordinates (x, y[, z, w]); x * element size
 // must be a multiple of 16 bytes.
 __device__ __forceinline__ void copy_tile_2d(void* smem_dst, const void* tensor_map, int x, int y, uint64_t* bar) {

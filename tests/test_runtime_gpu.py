@@ -34,8 +34,16 @@ def check_logits(got, ref):
     return 0.05 * std
 
 
+@pytest.fixture(params=[1, 0], ids=["persistent-decode-kernel", "kernel-per-phase"])
+def decode_path(b200p, request):
+    """The decode steps as one persistent cooperative kernel (opt-in) and as one kernel per phase (the default)."""
+    b200p.set_tuning("runtime_mega", request.param)
+    yield request.param
+    b200p.set_tuning("runtime_mega", -1)
+
+
 @pytest.mark.parametrize("cfg,kind,bias,T", [(SMALL, "bf16", False, 48), (SMALL, "f16", True, 33), (WIDE, "bf16", False, 130)])
-def test_prefill_and_teacher_forced_decode(b200p, torch_cuda, cfg, kind, bias, T):
+def test_prefill_and_teacher_forced_decode(b200p, torch_cuda, decode_path, cfg, kind, bias, T):
     torch = torch_cuda
     batch, max_seq, steps = 2, 192, 6
     w = rr.make_weights(cfg, seed=11, kind=kind, std=0.05, bias=bias)
@@ -55,11 +63,12 @@ def test_prefill_and_teacher_forced_decode(b200p, torch_cuda, cfg, kind, bias, T
         g, r = sess.step_logits(nxt), ref.step_logits(nxt)
         check_logits(g, r)
     assert b200p.device_status() == 0
+    assert (sess.mega_launches == steps) if decode_path else (sess.mega_launches == 0)
     sess.close()
 
 
 @pytest.mark.parametrize("batch", [3, 12])
-def test_generate_equals_stepwise_greedy(b200p, torch_cuda, batch):
+def test_generate_equals_stepwise_greedy(b200p, torch_cuda, decode_path, batch):
     """generate() keeps the next-token ids on the device; it must produce exactly the tokens
     of the host-driven loop over prefill_logits / step_logits on the same session.  Twelve
     sequences put the decode step on the projection kernels' two-fragment (9 .. 16 row) forms."""
@@ -72,6 +81,8 @@ def test_generate_equals_stepwise_greedy(b200p, torch_cuda, batch):
     toks, (ttft, dec) = sess.generate(ids, new)
     assert toks.shape == (batch, new) and ttft > 0 and dec > 0
     assert sess.kv_len == T + new - 1
+    # all decode steps of the call in one launch, for up to 8 sequences
+    assert sess.mega_launches == (1 if decode_path and batch <= 8 else 0)
     lg = sess.prefill_logits(ids)
     manual = np.zeros_like(toks)
     for s in range(new):
@@ -129,6 +140,42 @@ def test_generate_graph_replay_equals_launched_steps(b200p, torch_cuda):
     sess.close()
 
 
+@pytest.mark.parametrize("cfg,kind,T", [(SMALL, "bf16", 700), (WIDE, "f16", 1100)])
+def test_persistent_decode_kernel_over_a_long_cache(b200p, torch_cuda, cfg, kind, T):
+    """With more than 256 keys the persistent kernel's attention splits a (sequence, kv head) over several
+    CTAs that merge through global scratch.  Its logits against the kernel-per-phase path's on the same cache,
+    its tokens against its own host-driven loop, and a second call against the first (scratch and counters
+    are left clean)."""
+    torch = torch_cuda
+    batch, max_seq, new = 2, 2048, 24
+    w = rr.make_weights(cfg, seed=21, kind=kind, std=0.05)
+    sess = b200p.Session(cfg, to_device(torch, w, kind), max_seq, batch)
+    ids = np.random.default_rng(T).integers(0, cfg["vocab_size"], (batch, T)).astype(np.int32)
+    lg = sess.prefill_logits(ids)
+    nxt = np.argmax(orc.round_to(lg, kind), axis=-1).astype(np.int32)
+    b = sess.step_logits(nxt)                                  # kernel per phase
+    assert sess.mega_launches == 0
+    b200p.set_tuning("runtime_mega", 1)
+    try:
+        sess.prefill_logits(ids)
+        a = sess.step_logits(nxt)
+        assert sess.mega_launches == 1
+        check_logits(a, b)
+        toks, _ = sess.generate(ids, new)
+        lg = sess.prefill_logits(ids)
+        for s_ in range(new):
+            nx = np.argmax(orc.round_to(lg, kind), axis=-1).astype(np.int32)
+            assert np.array_equal(toks[:, s_], nx), s_
+            if s_ + 1 < new:
+                lg = sess.step_logits(nx)
+        again, _ = sess.generate(ids, new)
+        assert np.array_equal(toks, again)
+    finally:
+        b200p.set_tuning("runtime_mega", -1)
+    assert b200p.device_status() == 0
+    sess.close()
+
+
 # BASELINE config 5's dimensions (the Llama-style decoder of the reference's runtime benchmark)
 C5 = dict(hidden=2048, n_heads=32, n_kv_heads=4, head_dim=64, ffn_dim=5632, vocab_size=32000, rope_theta=10000.0)
 
@@ -156,9 +203,9 @@ def test_config5_dimensions_against_the_oracle(b200p, torch_cuda):
     sess.close()
 
 
-def test_config5_full_depth_generate_equals_stepwise(b200p, torch_cuda):
-    """All 22 layers at config 5 (2.2 GB of weights): generate() -- device-side greedy loop, captured step
-    graph -- gives exactly the tokens of the host-driven prefill_logits / step_logits loop
+def test_config5_full_depth_generate_equals_stepwise(b200p, torch_cuda, decode_path):
+    """All 22 layers at config 5 (2.2 GB of weights): generate() -- device-side greedy loop, as one persistent
+    kernel or as a captured step graph -- gives exactly the tokens of the host-driven prefill_logits / step_logits loop
     (cdna3-prims/include/cdna3/runtime/session.hpp:263-296)."""
     torch = torch_cuda
     cfg = dict(C5, n_layers=22)
@@ -174,7 +221,7 @@ def test_config5_full_depth_generate_equals_stepwise(b200p, torch_cuda):
     sess = b200p.Session(cfg, weights, T + new, batch)
     ids = np.random.default_rng(7).integers(0, cfg["vocab_size"], (batch, T)).astype(np.int32)
     toks, _ = sess.generate(ids, new)
-    assert sess.graph_replays == new - 2
+    assert (sess.mega_launches == 1 and sess.graph_replays == 0) if decode_path else (sess.graph_replays == new - 2)
     lg = sess.prefill_logits(ids)
     for s_ in range(new):
         nxt = np.argmax(orc.round_to(lg, "bf16"), axis=-1).astype(np.int32)
