@@ -74,53 +74,84 @@ template <int BACKEND> __device__ __forceinline__ float row_max(float a, float b
 }
 
 // which 0: y = (x - mean) / sqrt(var + eps) * gamma + beta;  which 1: y = softmax(x).  Row = 64 * E floats; lane l holds
-// the float2 at columns 64 e + 2 l (e = 0 .. E-1), so a warp reads whole 256-byte runs.
-template <int E, int BACKEND>
+// the float2 at columns 64 e + 2 l (e = 0 .. E-1), so a warp reads whole 256-byte runs.  A warp takes R consecutive
+// rows at a time, all their loads issued before the first reduction: with 64-column rows one row per warp leaves
+// 16 KB in flight per SM, a quarter of what the memory system needs to stay busy.
+template <int E, int R, int BACKEND>
 __global__ void __launch_bounds__(256)
 row_op_kernel(int which, const float* __restrict__ x, const float* __restrict__ gamma, const float* __restrict__ beta,
               float* __restrict__ out, int rows, float eps) {
-    const int row = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
-    if (row >= rows) return;
+    const int row0 = (blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32) * R;
+    if (row0 >= rows) return;
     const unsigned l = threadIdx.x % 32;
     constexpr int COLS = 64 * E;
-    const float2* xr = reinterpret_cast<const float2*>(x + size_t(row) * COLS);
-    float2 v[E];
+    float2 v[R][E];
     #pragma unroll
-    for (int e = 0; e < E; ++e) v[e] = xr[e * 32 + l];
-    float2* orow = reinterpret_cast<float2*>(out + size_t(row) * COLS);
+    for (int r = 0; r < R; ++r) {
+        const float2* xr = reinterpret_cast<const float2*>(x + size_t(min(row0 + r, rows - 1)) * COLS);
+        #pragma unroll
+        for (int e = 0; e < E; ++e) v[r][e] = xr[e * 32 + l];
+    }
     if (which == 0) {
-        float sa = 0.f, sb = 0.f;
+        float2 g[E], bt[E];
         #pragma unroll
-        for (int e = 0; e < E; ++e) { sa += v[e].x; sb += v[e].y; }
-        const float mean = row_sum<BACKEND>(sa, sb) * (1.f / COLS);
-        float qa = 0.f, qb = 0.f;
+        for (int e = 0; e < E; ++e) { g[e] = reinterpret_cast<const float2*>(gamma)[e * 32 + l]; bt[e] = reinterpret_cast<const float2*>(beta)[e * 32 + l]; }
+        float mean[R], inv[R];
         #pragma unroll
-        for (int e = 0; e < E; ++e) { const float dx = v[e].x - mean, dy = v[e].y - mean; qa += dx * dx; qb += dy * dy; }
-        const float inv = rsqrtf(row_sum<BACKEND>(qa, qb) * (1.f / COLS) + eps);
+        for (int r = 0; r < R; ++r) {
+            float sa = 0.f, sb = 0.f;
+            #pragma unroll
+            for (int e = 0; e < E; ++e) { sa += v[r][e].x; sb += v[r][e].y; }
+            mean[r] = row_sum<BACKEND>(sa, sb) * (1.f / COLS);
+        }
         #pragma unroll
-        for (int e = 0; e < E; ++e) {
-            const float2 g = reinterpret_cast<const float2*>(gamma)[e * 32 + l], bt = reinterpret_cast<const float2*>(beta)[e * 32 + l];
-            orow[e * 32 + l] = make_float2((v[e].x - mean) * inv * g.x + bt.x, (v[e].y - mean) * inv * g.y + bt.y);
+        for (int r = 0; r < R; ++r) {
+            float qa = 0.f, qb = 0.f;
+            #pragma unroll
+            for (int e = 0; e < E; ++e) { const float dx = v[r][e].x - mean[r], dy = v[r][e].y - mean[r]; qa += dx * dx; qb += dy * dy; }
+            inv[r] = rsqrtf(row_sum<BACKEND>(qa, qb) * (1.f / COLS) + eps);
+        }
+        #pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (row0 + r < rows) {
+                float2* orow = reinterpret_cast<float2*>(out + size_t(row0 + r) * COLS);
+                #pragma unroll
+                for (int e = 0; e < E; ++e)
+                    orow[e * 32 + l] = make_float2((v[r][e].x - mean[r]) * inv[r] * g[e].x + bt[e].x, (v[r][e].y - mean[r]) * inv[r] * g[e].y + bt[e].y);
+            }
         }
     } else {
-        float ma = v[0].x, mb = v[0].y;
+        float m[R], inv[R];
         #pragma unroll
-        for (int e = 1; e < E; ++e) { ma = fmaxf(ma, v[e].x); mb = fmaxf(mb, v[e].y); }
-        const float m = row_max<BACKEND>(ma, mb);
-        float sa = 0.f, sb = 0.f;
+        for (int r = 0; r < R; ++r) {
+            float ma = v[r][0].x, mb = v[r][0].y;
+            #pragma unroll
+            for (int e = 1; e < E; ++e) { ma = fmaxf(ma, v[r][e].x); mb = fmaxf(mb, v[r][e].y); }
+            m[r] = row_max<BACKEND>(ma, mb);
+        }
         #pragma unroll
-        for (int e = 0; e < E; ++e) { v[e].x = __expf(v[e].x - m); v[e].y = __expf(v[e].y - m); sa += v[e].x; sb += v[e].y; }
-        const float inv = 1.f / row_sum<BACKEND>(sa, sb);
+        for (int r = 0; r < R; ++r) {
+            float sa = 0.f, sb = 0.f;
+            #pragma unroll
+            for (int e = 0; e < E; ++e) { v[r][e].x = __expf(v[r][e].x - m[r]); v[r][e].y = __expf(v[r][e].y - m[r]); sa += v[r][e].x; sb += v[r][e].y; }
+            inv[r] = 1.f / row_sum<BACKEND>(sa, sb);
+        }
         #pragma unroll
-        for (int e = 0; e < E; ++e) orow[e * 32 + l] = make_float2(v[e].x * inv, v[e].y * inv);
+        for (int r = 0; r < R; ++r) {
+            if (row0 + r < rows) {
+                float2* orow = reinterpret_cast<float2*>(out + size_t(row0 + r) * COLS);
+                #pragma unroll
+                for (int e = 0; e < E; ++e) orow[e * 32 + l] = make_float2(v[r][e].x * inv[r], v[r][e].y * inv[r]);
+            }
+        }
     }
 }
 
-template <int E>
+template <int E, int R>
 int launch_row(int which, int backend, const float* x, const float* g, const float* b, float* out, int rows, float eps, cudaStream_t st) {
-    const int grid = (rows + 7) / 8;
-    if (backend == 0) row_op_kernel<E, 0><<<grid, 256, 0, st>>>(which, x, g, b, out, rows, eps);
-    else              row_op_kernel<E, 1><<<grid, 256, 0, st>>>(which, x, g, b, out, rows, eps);
+    const int grid = (rows + 8 * R - 1) / (8 * R);
+    if (backend == 0) row_op_kernel<E, R, 0><<<grid, 256, 0, st>>>(which, x, g, b, out, rows, eps);
+    else              row_op_kernel<E, R, 1><<<grid, 256, 0, st>>>(which, x, g, b, out, rows, eps);
     return launched();
 }
 
@@ -154,6 +185,6 @@ extern "C" int b200p_row_op(int which, int backend, int cols, const float* x, co
     if (!aligned(x, 8) || !aligned(out, 8) || (which == 0 && (!aligned(gamma, 8) || !aligned(beta, 8)))) return B200P_E_ALIGN;
     if (sm_count() <= 0) return B200P_E_NO_DEVICE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
-    return cols == 64 ? launch_row<1>(which, backend, x, gamma, beta, out, rows, eps, st)
-                      : launch_row<8>(which, backend, x, gamma, beta, out, rows, eps, st);
+    return cols == 64 ? launch_row<1, 8>(which, backend, x, gamma, beta, out, rows, eps, st)
+                      : launch_row<8, 1>(which, backend, x, gamma, beta, out, rows, eps, st);
 }
