@@ -66,6 +66,42 @@ int launch_loop(int op, const void* in, void* out, int waves, int reps, cudaStre
     return launched();
 }
 
+// The scan loop (research/wave-primitives/benchmarks/bench_scan_dpp.hip): every wave takes the inclusive prefix
+// sum of its 64 values `reps` times, the last element fed back into the next round's inputs.  Backend 0:
+// wave::dpp::scan_inclusive_sum on the pair; backend 1: the portable form (pair prefix, shuffle-up ladder over the
+// lanes' totals, add the exclusive lane prefix).
+template <typename T>
+__device__ __forceinline__ void portable_pair_scan(T& a, T& b) {
+    b = a + b;
+    T t = b;
+    const unsigned l = threadIdx.x % 32;
+    #pragma unroll
+    for (int o = 1; o < 32; o <<= 1) { const T u = __shfl_up_sync(0xffffffffu, t, o); if (l >= unsigned(o)) t = t + u; }
+    const T excl = t - b;
+    a = a + excl; b = b + excl;
+}
+template <typename T, int BACKEND>
+__global__ void __launch_bounds__(256)
+wave_scan_loop_kernel(const T* __restrict__ in, T* __restrict__ out, int reps) {
+    const size_t wave_i = size_t(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    const unsigned l = threadIdx.x % 32;
+    T a = in[wave_i * 64 + 2 * l], b = in[wave_i * 64 + 2 * l + 1];
+    T acc = T(0);
+    #pragma unroll 1
+    for (int r = 0; r < reps; ++r) {
+        if (BACKEND == 0) wave::dpp::scan_inclusive_sum(a, b);
+        else              portable_pair_scan(a, b);
+        acc = acc + b;                                           // lane 31 holds the wave's total in b
+        const T last = __shfl_sync(0xffffffffu, b, 31);
+        // next round: small values that depend on this round's result (the total's parity for integers, its sign for floats)
+        const T dep = last > T(0) ? T(1) : T(0);
+        a = T((2 * l) % 5) + dep;
+        b = T((2 * l + 1) % 5) + dep;
+    }
+    out[wave_i * 64 + 2 * l] = a + acc;                          // every lane's state is observable
+    out[wave_i * 64 + 2 * l + 1] = b;
+}
+
 template <int BACKEND> __device__ __forceinline__ float row_sum(float a, float b) {
     return BACKEND == 0 ? wave::dpp::reduce_sum_bcast(a, b) : portable_pair_reduce_bcast(a, b, wave::SumOp{});
 }
@@ -174,6 +210,27 @@ extern "C" int b200p_wave_reduce_loop(int op, int dtype, int backend, const void
         case B200P_I32: return backend == 0 ? launch_loop<int, 0>(op, in, out, n_waves, reps, st) : launch_loop<int, 1>(op, in, out, n_waves, reps, st);
         default:        return backend == 0 ? launch_loop<long long, 0>(op, in, out, n_waves, reps, st) : launch_loop<long long, 1>(op, in, out, n_waves, reps, st);
     }
+}
+
+extern "C" int b200p_wave_scan_loop(int dtype, int backend, const void* in, void* out, int n_waves, int reps, b200p_stream_t stream) {
+    if (backend != 0 && backend != 1) return B200P_E_OP;
+    if (dtype < B200P_F32 || dtype > B200P_I64) return B200P_E_DTYPE;
+    if (n_waves <= 0 || n_waves % 8 != 0 || reps <= 0) return B200P_E_LENGTH;
+    if (!in || !out) return B200P_E_NULL;
+    if (sm_count() <= 0) return B200P_E_NO_DEVICE;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    const int grid = n_waves / 8;
+    #define B200P_SCAN_LOOP(T) \
+        if (backend == 0) wave_scan_loop_kernel<T, 0><<<grid, 256, 0, st>>>(static_cast<const T*>(in), static_cast<T*>(out), reps); \
+        else              wave_scan_loop_kernel<T, 1><<<grid, 256, 0, st>>>(static_cast<const T*>(in), static_cast<T*>(out), reps);
+    switch (dtype) {
+        case B200P_F32: B200P_SCAN_LOOP(float) break;
+        case B200P_F64: B200P_SCAN_LOOP(double) break;
+        case B200P_I32: B200P_SCAN_LOOP(int) break;
+        default:        B200P_SCAN_LOOP(long long) break;
+    }
+    #undef B200P_SCAN_LOOP
+    return launched();
 }
 
 extern "C" int b200p_row_op(int which, int backend, int cols, const float* x, const float* gamma, const float* beta, float* out,

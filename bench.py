@@ -835,7 +835,22 @@ class WaveApi:
                     torch.cuda.synchronize()
                     ms = sorted(a.elapsed_time(b) for a, b in ts)[10]
                     out[f"reduce_{op}<{name}> {backend}"] = round(64.0 * waves * reps / (ms * 1e-3) / 1e9, 1)
-        return {"wave_reduce_loop_Gelem_per_s": out}
+        scan = {}
+        for dt, name in ((torch.float32, "f32"), (torch.int32, "i32"), (torch.float64, "f64")):
+            x = ((torch.arange(64 * waves, device=self.x[64].device) % 3) - 1).to(dt)
+            o = torch.empty_like(x)
+            for backend in ("primitives", "portable"):
+                for _ in range(3):
+                    pkg.wave_scan_loop(x, reps, backend, out=o)
+                ts = []
+                for _ in range(20):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(); pkg.wave_scan_loop(x, reps, backend, out=o); b.record()
+                    ts.append((a, b))
+                torch.cuda.synchronize()
+                ms = sorted(a.elapsed_time(b) for a, b in ts)[10]
+                scan[f"scan_inclusive_sum<{name}> {backend}"] = round(64.0 * waves * reps / (ms * 1e-3) / 1e9, 1)
+        return {"wave_reduce_loop_Gelem_per_s": out, "wave_scan_loop_Gelem_per_s": scan}
 
     def cpu_run(self, orc, n, threads, reps=1):
         """n = thousands of rows of 512 columns: numpy LayerNorm + softmax (the CPU statement of the two row kernels)."""

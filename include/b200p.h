@@ -117,6 +117,12 @@ int b200p_wave_vote_probe(const int* in64, unsigned long long* out8, b200p_strea
 int b200p_wave_reduce_loop(int op, int dtype, int backend, const void* in, void* out, int n_waves, int reps,
                            b200p_stream_t stream);
 
+/* The same for the inclusive prefix sum (research/wave-primitives/benchmarks/bench_scan_dpp.hip): each wave scans its
+ * 64 values `reps` times, the total fed back into the next round's inputs.  in and out: 64 * n_waves values (out
+ * receives the waves' final state).  backend 0: wave::dpp::scan_inclusive_sum (pair per lane); backend 1: the
+ * portable shuffle-up ladder.  f32 / f64 / i32 / i64.  Throughput = 64 * n_waves * reps elements per launch. */
+int b200p_wave_scan_loop(int dtype, int backend, const void* in, void* out, int n_waves, int reps, b200p_stream_t stream);
+
 /* The reference's two "real kernel" benchmarks of the primitives, one wave per row
  * (research/wave-primitives/benchmarks/bench_layernorm.hip:47-96, bench_softmax.hip):
  * which 0: out = LayerNorm(x) * gamma + beta (two row sums);  which 1: out = softmax(x) (row max + row sum).

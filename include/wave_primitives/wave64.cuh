@@ -70,6 +70,15 @@ __device__ __forceinline__ unsigned lane_id() {
     asm("mov.u32 %0, %%laneid;" : "=r"(id));
     return id;
 }
+// The lane index read afresh at every call (volatile: never hoisted out of a caller's loop).  The scans select on
+// the lane index; when that index is loop-invariant the compiler may unswitch the caller's loop on it and give
+// lane 0 a loop body of its own -- legal, but the full-mask shuffles of the two bodies then meet from different
+// program counters and take ~300 cycles each (a 32-bit pair scan in a loop: 1900 cycles instead of 250).
+__device__ __forceinline__ unsigned lane_id_here() {
+    unsigned id;
+    asm volatile("mov.u32 %0, %%laneid;" : "=r"(id));
+    return id;
+}
 namespace detail {
 __device__ __forceinline__ float redux_max_f32(unsigned m, float v) { float r; asm volatile("redux.sync.max.f32 %0, %1, %2;" : "=f"(r) : "f"(v), "r"(m)); return r; }
 __device__ __forceinline__ float redux_min_f32(unsigned m, float v) { float r; asm volatile("redux.sync.min.f32 %0, %1, %2;" : "=f"(r) : "f"(v), "r"(m)); return r; }
@@ -214,7 +223,7 @@ template <int VEC, int ROW, typename T, typename Op>
 __device__ __forceinline__ void row_scan_kogge_stone(T (&v)[VEC], Op op, T identity) {
     constexpr int LPR = ROW / VEC;                 // lanes per row
     static_assert(LPR >= 1 && LPR <= 32, "row must fit a warp");
-    const unsigned q = lane_id() & unsigned(LPR - 1);   // lane position inside its row
+    const unsigned q = lane_id_here() & unsigned(LPR - 1);   // lane position inside its row
     #pragma unroll
     for (int o = 1; o < ROW; o <<= 1) {
         T old[VEC];
@@ -271,7 +280,7 @@ __device__ __forceinline__ void segment_scan_dpp_order(T (&v)[VEC], Op op, T ide
     constexpr int LPS = kSegment / VEC;            // lanes per segment
     constexpr int LPR = 16 / VEC;                  // lanes per 16-element row
     row_scan_kogge_stone<VEC, 16>(v, op, identity);
-    const unsigned lane = lane_id();
+    const unsigned lane = lane_id_here();
     const unsigned seg0 = lane & ~unsigned(LPS - 1);
     const unsigned row  = (lane & unsigned(LPS - 1)) / unsigned(LPR);
     // Row totals sit on the last element of the last lane of each row.
@@ -280,14 +289,14 @@ __device__ __forceinline__ void segment_scan_dpp_order(T (&v)[VEC], Op op, T ide
     const T t2 = detail::shfl_idx(v[VEC - 1], int(seg0 + 3 * LPR - 1));
     // c1 / c1b / c1c of the reference: the totals of the 1st, 2nd, 3rd row
     // below this one, combined nearest-first.
-    T carry = identity;
-    if (row == 1u) carry = t0;
-    if (row == 2u) carry = op(t1, t0);
-    if (row == 3u) carry = op(op(t2, t1), t0);
-    if (row >= 1u) {
-        #pragma unroll
-        for (int j = 0; j < VEC; ++j) v[j] = op(v[j], carry);
+    const T c2 = op(t1, t0), c3 = op(op(t2, t1), t0);
+    const T carry = row == 1u ? t0 : row == 2u ? c2 : c3;
+    #pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+        const T w = op(v[j], carry);
+        v[j] = row >= 1u ? w : v[j];
     }
+    (void)identity;
 }
 
 // ---------------------------------------------------------------------------
@@ -300,18 +309,27 @@ __device__ __forceinline__ void segment_scan_fast(T (&v)[VEC], Op op, T identity
     constexpr int LPS = kSegment / VEC;
     #pragma unroll
     for (int j = 1; j < VEC; ++j) v[j] = op(v[j], v[j - 1]);
-    const unsigned q = lane_id() & unsigned(LPS - 1);
+    const unsigned q = lane_id_here() & unsigned(LPS - 1);
     T tot = v[VEC - 1];
+    // every lane runs the same instructions: lanes a step does not apply to keep their value through a select
     #pragma unroll
     for (int d = 1; d < LPS; d <<= 1) {
-        T up = detail::shfl_up(tot, unsigned(d));
-        if (q >= unsigned(d)) tot = op(tot, up);
+        const T up = detail::shfl_up(tot, unsigned(d));
+        const T sum = op(tot, up);
+        tot = q >= unsigned(d) ? sum : tot;
     }
-    T excl = detail::shfl_up(tot, 1);
-    if (q == 0u) excl = identity;
-    if (q != 0u) {
+    if constexpr (std::is_same<Op, SumOp>::value && std::is_integral<T>::value) {
+        // wrapping integer sums have an inverse: the exclusive prefix is the inclusive one minus the lane's own total
+        const T excl = tot - v[VEC - 1];
         #pragma unroll
-        for (int j = 0; j < VEC; ++j) v[j] = op(v[j], excl);
+        for (int j = 0; j < VEC; ++j) v[j] = v[j] + excl;
+    } else {
+        const T excl = detail::shfl_up(tot, 1);
+        #pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            const T w = op(v[j], excl);
+            v[j] = q != 0u ? w : v[j];
+        }
     }
     (void)identity;
 }
@@ -321,7 +339,7 @@ __device__ __forceinline__ void segment_scan_fast(T (&v)[VEC], Op op, T identity
 template <int VEC, typename T>
 __device__ __forceinline__ void segment_shift_right(T (&v)[VEC], T first) {
     constexpr int LPS = kSegment / VEC;
-    const unsigned q = lane_id() & unsigned(LPS - 1);
+    const unsigned q = lane_id_here() & unsigned(LPS - 1);
     T prev = detail::shfl_up(v[VEC - 1], 1);
     if (q == 0u) prev = first;
     #pragma unroll
@@ -382,11 +400,12 @@ template <typename T> __device__ __forceinline__ T reduce_min_bcast(T v) { retur
 
 template <typename T, typename Op>
 __device__ __forceinline__ T warp_scan_inclusive(T v, Op op) {
-    const unsigned l = lane_id();
+    const unsigned l = lane_id_here();
     #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-        T u = detail::shfl_up(v, unsigned(o));
-        if (l >= unsigned(o)) v = op(v, u);
+        const T u = detail::shfl_up(v, unsigned(o));
+        const T w = op(v, u);
+        v = l >= unsigned(o) ? w : v;
     }
     return v;
 }
@@ -396,7 +415,7 @@ template <typename T> __device__ __forceinline__ T scan_inclusive_min(T v) { ret
 template <typename T> __device__ __forceinline__ T scan_exclusive_sum(T v) {
     T inc = scan_inclusive_sum(v);
     T ex = detail::shfl_up(inc, 1);
-    return lane_id() == 0u ? T(0) : ex;
+    return lane_id_here() == 0u ? T(0) : ex;
 }
 
 } // namespace dpp

@@ -55,6 +55,7 @@ inline int __reduce_min_sync(unsigned m, int v) { return warp_shim::group_reduce
 
 namespace wave {
 inline unsigned lane_id() { return warp_shim::t_lane; }
+inline unsigned lane_id_here() { return warp_shim::t_lane; }
 namespace detail {
 inline float redux_max_f32(unsigned m, float v) { return warp_shim::group_reduce(m, v, [](float a, float b) { return a > b ? a : b; }); }
 inline float redux_min_f32(unsigned m, float v) { return warp_shim::group_reduce(m, v, [](float a, float b) { return a < b ? a : b; }); }

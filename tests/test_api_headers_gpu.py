@@ -69,6 +69,27 @@ def test_register_resident_reduce_loop(b200p, torch_cuda, dt, backend):
 
 
 @pytest.mark.parametrize("backend", ["primitives", "portable"])
+@pytest.mark.parametrize("dt", ["float32", "float64", "int32", "int64"])
+def test_register_resident_scan_loop(b200p, torch_cuda, dt, backend):
+    """The scan loop computes what a host loop computes (small integer-valued data: exact in every type)."""
+    torch = torch_cuda
+    dtype = getattr(torch, dt)
+    waves, reps = 64, 4
+    x = (torch.arange(64 * waves, device="cuda") % 3).to(dtype) - 1          # -1, 0, 1: totals of either sign
+    got = b200p.wave_scan_loop(x, reps, backend).view(waves, 64)
+    v = x.view(waves, 64).clone()
+    acc = torch.zeros(waves, 32, device="cuda", dtype=dtype)                 # per lane: sum of its second element over the rounds
+    idx = torch.arange(64, device="cuda")
+    for _ in range(reps):
+        sc = torch.cumsum(v, dim=1).to(dtype)
+        acc = acc + sc[:, 1::2]
+        dep = (sc[:, 63:64] > 0).to(dtype)
+        v = ((idx % 5).to(dtype)[None, :] + dep).to(dtype)
+    assert torch.equal(got[:, 1::2], v[:, 1::2]), dt
+    assert torch.equal(got[:, 0::2], v[:, 0::2] + acc), dt
+
+
+@pytest.mark.parametrize("backend", ["primitives", "portable"])
 @pytest.mark.parametrize("cols", [64, 512])
 def test_layernorm_and_softmax_rows(b200p, torch_cuda, cols, backend):
     torch = torch_cuda
