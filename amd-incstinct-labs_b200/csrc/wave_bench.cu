@@ -54,6 +54,35 @@ wave_reduce_loop_kernel(const T* __restrict__ in, T* __restrict__ out, int reps)
     if (l == 31) out[wave_i] = acc;
 }
 
+// 16-bit inputs: the sum is accumulated in fp32 and rounded once (wave::reduce_sum(__half / bf16 pair),
+// research/wave-primitives/benchmarks/bench_h3_h4_multitype.hip's fp32-acc form); backend 1 accumulates in the 16-bit
+// type itself with the portable shuffle-down loop (the "native" form the reference compares against).
+template <typename T, int BACKEND>
+__global__ void __launch_bounds__(256)
+wave_reduce_loop16_kernel(const T* __restrict__ in, T* __restrict__ out, int reps) {
+    const size_t wave_i = size_t(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+    const unsigned l = threadIdx.x % 32;
+    T a = in[wave_i * 64 + 2 * l], b = in[wave_i * 64 + 2 * l + 1];
+    float acc = 0.f;
+    #pragma unroll 1
+    for (int r = 0; r < reps; ++r) {
+        T s;
+        if (BACKEND == 0) s = wave::reduce_sum(a, b);
+        else {
+            T v = a + b;
+            #pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v = v + __shfl_down_sync(0xffffffffu, v, o);
+            s = __shfl_sync(0xffffffffu, v, 0);
+        }
+        acc += float(s);
+        // next round: small values that depend on this round's result
+        const T dep = float(s) > 100.f ? T(1.f) : T(0.f);
+        a = T(float((2 * l) % 5)) + dep;
+        b = T(float((2 * l + 1) % 5)) + dep;
+    }
+    if (l == 31) out[wave_i] = T(acc);
+}
+
 template <typename T, int BACKEND>
 int launch_loop(int op, const void* in, void* out, int waves, int reps, cudaStream_t st) {
     const int grid = waves / 8;
@@ -199,11 +228,24 @@ using namespace b200p;
 extern "C" int b200p_wave_reduce_loop(int op, int dtype, int backend, const void* in, void* out, int n_waves, int reps,
                                       b200p_stream_t stream) {
     if (op < B200P_SUM || op > B200P_MIN || (backend != 0 && backend != 1)) return B200P_E_OP;
-    if (dtype < B200P_F32 || dtype > B200P_I64) return B200P_E_DTYPE;
+    const bool narrow = dtype == B200P_F16 || dtype == B200P_BF16;
+    if (!narrow && (dtype < B200P_F32 || dtype > B200P_I64)) return B200P_E_DTYPE;
+    if (narrow && op != B200P_SUM) return B200P_E_OP;
     if (n_waves <= 0 || n_waves % 8 != 0 || reps <= 0) return B200P_E_LENGTH;
     if (!in || !out) return B200P_E_NULL;
     if (sm_count() <= 0) return B200P_E_NO_DEVICE;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (narrow) {
+        const int grid = n_waves / 8;
+        if (dtype == B200P_F16) {
+            if (backend == 0) wave_reduce_loop16_kernel<__half, 0><<<grid, 256, 0, st>>>(static_cast<const __half*>(in), static_cast<__half*>(out), reps);
+            else              wave_reduce_loop16_kernel<__half, 1><<<grid, 256, 0, st>>>(static_cast<const __half*>(in), static_cast<__half*>(out), reps);
+        } else {
+            if (backend == 0) wave_reduce_loop16_kernel<__nv_bfloat16, 0><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), reps);
+            else              wave_reduce_loop16_kernel<__nv_bfloat16, 1><<<grid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), static_cast<__nv_bfloat16*>(out), reps);
+        }
+        return launched();
+    }
     switch (dtype) {
         case B200P_F32: return backend == 0 ? launch_loop<float, 0>(op, in, out, n_waves, reps, st) : launch_loop<float, 1>(op, in, out, n_waves, reps, st);
         case B200P_F64: return backend == 0 ? launch_loop<double, 0>(op, in, out, n_waves, reps, st) : launch_loop<double, 1>(op, in, out, n_waves, reps, st);

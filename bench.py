@@ -835,6 +835,20 @@ class WaveApi:
                     torch.cuda.synchronize()
                     ms = sorted(a.elapsed_time(b) for a, b in ts)[10]
                     out[f"reduce_{op}<{name}> {backend}"] = round(64.0 * waves * reps / (ms * 1e-3) / 1e9, 1)
+        for dt, name in ((torch.float16, "f16"), (torch.bfloat16, "bf16")):
+            x = (torch.arange(64 * waves, device=self.x[64].device) % 7).to(dt)
+            o = torch.empty(waves, dtype=dt, device=x.device)
+            for backend, label in (("primitives", "fp32 accumulation (primitives)"), ("portable", "16-bit accumulation (portable)")):
+                for _ in range(3):
+                    pkg.wave_reduce_loop(x, "sum", reps, backend, out=o)
+                ts = []
+                for _ in range(20):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(); pkg.wave_reduce_loop(x, "sum", reps, backend, out=o); b.record()
+                    ts.append((a, b))
+                torch.cuda.synchronize()
+                ms = sorted(a.elapsed_time(b) for a, b in ts)[10]
+                out[f"reduce_sum<{name}> {label}"] = round(64.0 * waves * reps / (ms * 1e-3) / 1e9, 1)
         scan = {}
         for dt, name in ((torch.float32, "f32"), (torch.int32, "i32"), (torch.float64, "f64")):
             x = ((torch.arange(64 * waves, device=self.x[64].device) % 3) - 1).to(dt)

@@ -112,7 +112,9 @@ int b200p_wave_vote_probe(const int* in64, unsigned long long* out8, b200p_strea
  * (research/wave-primitives/benchmarks/bench_reduce_dpp_types.hip:29-45): each of n_waves waves (a multiple of 8;
  * in: 64 * n_waves values, out: n_waves values) reduces its 64 values `reps` times with the result fed back into
  * the inputs, no memory traffic inside the loop.  backend 0: wave::dpp::reduce_* of wave64.cuh (pair per lane);
- * backend 1: the portable shuffle-down loop + broadcast the reference compares against.  f32 / f64 / i32 / i64.
+ * backend 1: the portable shuffle-down loop + broadcast the reference compares against.  f32 / f64 / i32 / i64;
+ * f16 / bf16 for the sum only (bench_h3_h4_multitype.hip): backend 0 accumulates in fp32 and rounds once
+ * (wave::reduce_sum on a 16-bit pair), backend 1 accumulates in the 16-bit type (the "native" form).
  * The caller times the launch; throughput = 64 * n_waves * reps elements per launch. */
 int b200p_wave_reduce_loop(int op, int dtype, int backend, const void* in, void* out, int n_waves, int reps,
                            b200p_stream_t stream);

@@ -68,6 +68,27 @@ def test_register_resident_reduce_loop(b200p, torch_cuda, dt, backend):
         assert torch.equal(got, acc), (dt, op)
 
 
+@pytest.mark.parametrize("dt", ["float16", "bfloat16"])
+def test_register_resident_reduce_loop_16bit_fp32_accumulation(b200p, torch_cuda, dt):
+    """16-bit inputs, fp32 accumulation, one rounding (wave::reduce_sum on a 16-bit pair) against the same in torch;
+    the small integer values keep both exact."""
+    torch = torch_cuda
+    dtype = getattr(torch, dt)
+    waves, reps = 64, 5
+    x = (torch.arange(64 * waves, device="cuda") % 7).to(dtype)
+    got = b200p.wave_reduce_loop(x, "sum", reps, "primitives")
+    v, acc = x.view(waves, 64).clone(), torch.zeros(waves, device="cuda", dtype=torch.float32)
+    idx = torch.arange(64, device="cuda")
+    for _ in range(reps):
+        s = v.float().sum(dim=1).to(dtype)
+        acc = acc + s.float()
+        dep = (s.float() > 100.0).to(dtype)
+        v = ((idx % 5).to(dtype)[None, :] + dep[:, None]).to(dtype)
+    assert torch.equal(got, acc.to(dtype)), dt
+    native = b200p.wave_reduce_loop(x, "sum", reps, "portable")               # 16-bit accumulation: same here, the sums are small integers
+    assert torch.equal(native, got), dt
+
+
 @pytest.mark.parametrize("backend", ["primitives", "portable"])
 @pytest.mark.parametrize("dt", ["float32", "float64", "int32", "int64"])
 def test_register_resident_scan_loop(b200p, torch_cuda, dt, backend):
