@@ -299,6 +299,54 @@ class DecodeGQA:
     def e2e_bytes(self):
         return self.q_host.numel() * 2, self.o_host.numel() * 2
 
+    def extra_fields(self):
+        """The reference's own decode table: batch 1, D 128, GQA 32q / 8kv, fp16, N = 256 .. 8192 keys; us per launch
+        (median of 20, one event pair each) next to the reference's MI300X time."""
+        torch, pkg = self.torch, self.pkg
+        ref_us = {256: 18.1, 512: 32.2, 1024: 60.4, 2048: 118.7, 4096: 384.5, 8192: 803.4}
+        out = {}
+        for n, r in ref_us.items():
+            g = torch.Generator(device=self.q.device); g.manual_seed(0xB204 + n)
+            q = torch.randn(1, 32, 128, device=self.q.device, generator=g).half()
+            K = torch.randn(1, 8, n, 128, device=self.q.device, generator=g).half()
+            V = torch.randn(1, 8, n, 128, device=self.q.device, generator=g).half()
+            o = torch.empty_like(q)
+            ws = pkg.decode_workspace(q, K)
+            for _ in range(3):
+                pkg.decode(q, K, V, out=o, workspace=ws)
+            ts = []
+            for _ in range(20):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(); pkg.decode(q, K, V, out=o, workspace=ws); b.record()
+                ts.append((a, b))
+            torch.cuda.synchronize()
+            us = sorted(a.elapsed_time(b) for a, b in ts)[10] * 1e3
+            e = {"us_per_call_from_python": round(us, 1), "reference_mi300x_us": r}
+            # a launch of this size is shorter than a Python call: the device time is that of 20 calls captured in
+            # one CUDA graph and replayed (the reference times a C++ loop of launches)
+            try:
+                side = torch.cuda.Stream(device=self.q.device)
+                side.wait_stream(torch.cuda.current_stream())
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(side):
+                    with torch.cuda.graph(graph, stream=side):
+                        for _ in range(20):
+                            pkg.decode(q, K, V, out=o, workspace=ws)
+                    graph.replay()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(side)
+                    for _ in range(5):
+                        graph.replay()
+                    b.record(side)
+                b.synchronize()
+                e["us"] = round(a.elapsed_time(b) * 1e3 / 100, 2)
+                torch.cuda.current_stream().wait_stream(side)
+                del graph
+            except Exception as ex:                                   # capture not possible: keep the per-call figure
+                e["us"] = e["us_per_call_from_python"]; e["graph"] = f"unavailable: {type(ex).__name__}"
+            out[f"batch1_gqa32q8kv_d128_n{n}"] = e
+        return {"reference_shapes": out}
+
     def cpu_run(self, orc, n, threads, reps=1):
         """n = sequences of the batch (full kv length)."""
         import numpy as np
@@ -397,7 +445,32 @@ class PrefillCausal:
             ms = a.elapsed_time(b) / 10
             out[label] = {"ms": round(ms, 4), "TFLOP/s": round(4.0 * B * H * S * S * D * (0.5 if causal else 1.0) / ms / 1e9, 1)}
             del q, k, v, o
-        return {"other_shapes": out}
+        # the shapes of the reference's own prefill tables (batch 1, D 128, fp16): MHA 8 heads non-causal and GQA 32q/8kv
+        # causal at 512 .. 4096 tokens; us per launch (median of 20, one event pair each), next to the reference's MI300X time
+        ref_us = {("mha8_full", 512): 103.7, ("mha8_full", 4096): 6015.1,
+                  ("gqa32q8kv_causal", 512): 389.5, ("gqa32q8kv_causal", 1024): 1051.9, ("gqa32q8kv_causal", 2048): 3407.9, ("gqa32q8kv_causal", 4096): 11829.4}
+        ref = {}
+        for kind, H, hkv, causal in (("mha8_full", 8, 8, False), ("gqa32q8kv_causal", 32, 8, True)):
+            for S in (512, 1024, 2048, 4096):
+                g = torch.Generator(device=self.Q.device); g.manual_seed(0xB203 + S + H)
+                q = (torch.randn(1, H, S, 128, device=self.Q.device, generator=g) * 0.5).half()
+                k = (torch.randn(1, hkv, S, 128, device=self.Q.device, generator=g) * 0.5).half()
+                v = (torch.randn(1, hkv, S, 128, device=self.Q.device, generator=g) * 0.5).half()
+                o = torch.empty_like(q)
+                for _ in range(3):
+                    pkg.prefill(q, k, v, causal=causal, out=o)
+                ts = []
+                for _ in range(20):
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(); pkg.prefill(q, k, v, causal=causal, out=o); b.record()
+                    ts.append((a, b))
+                torch.cuda.synchronize()
+                us = sorted(a.elapsed_time(b) for a, b in ts)[10] * 1e3
+                e = {"us": round(us, 1), "TFLOP/s": round(4.0 * H * S * S * 128 * (0.5 if causal else 1.0) / us / 1e6, 1)}
+                if (kind, S) in ref_us:
+                    e["reference_mi300x_us"] = ref_us[(kind, S)]
+                ref[f"{kind}_s{S}"] = e
+        return {"other_shapes": out, "reference_shapes": ref}
 
     def cpu_run(self, orc, n, threads, reps=1):
         """n = (batch, head) units at full sequence length."""
