@@ -47,7 +47,7 @@ wave_reduce_loop_kernel(const T* __restrict__ in, T* __restrict__ out, int reps)
             else              s = portable_pair_reduce_bcast(a, b, wave::MinOp{});
         }
         acc = acc + s;
-        // per-lane perturbation: the next round's inputs depend on this round's result
+        // per-lane perturbation: the inputs of the next repetition depend on this one's result
         a = s + T(2 * l) + T(1);
         b = s + T(2 * l + 1) + T(1);
     }
@@ -75,7 +75,7 @@ wave_reduce_loop16_kernel(const T* __restrict__ in, T* __restrict__ out, int rep
             s = __shfl_sync(0xffffffffu, v, 0);
         }
         acc += float(s);
-        // next round: small values that depend on this round's result
+        // next repetition: small values that depend on this one's result
         const T dep = float(s) > 100.f ? T(1.f) : T(0.f);
         a = T(float((2 * l) % 5)) + dep;
         b = T(float((2 * l + 1) % 5)) + dep;
@@ -96,7 +96,7 @@ int launch_loop(int op, const void* in, void* out, int waves, int reps, cudaStre
 }
 
 // The scan loop (research/wave-primitives/benchmarks/bench_scan_dpp.hip): every wave takes the inclusive prefix
-// sum of its 64 values `reps` times, the last element fed back into the next round's inputs.  Backend 0:
+// sum of its 64 values `reps` times, the last element fed back into the inputs of the next repetition.  Backend 0:
 // wave::dpp::scan_inclusive_sum on the pair; backend 1: the portable form (pair prefix, shuffle-up ladder over the
 // lanes' totals, add the exclusive lane prefix).
 template <typename T>
@@ -122,7 +122,7 @@ wave_scan_loop_kernel(const T* __restrict__ in, T* __restrict__ out, int reps) {
         else              portable_pair_scan(a, b);
         acc = acc + b;                                           // lane 31 holds the wave's total in b
         const T last = __shfl_sync(0xffffffffu, b, 31);
-        // next round: small values that depend on this round's result (the total's parity for integers, its sign for floats)
+        // next repetition: small values that depend on this one's result (the total's parity for integers, its sign for floats)
         const T dep = last > T(0) ? T(1) : T(0);
         a = T((2 * l) % 5) + dep;
         b = T((2 * l + 1) % 5) + dep;

@@ -120,7 +120,7 @@ int b200p_wave_reduce_loop(int op, int dtype, int backend, const void* in, void*
                            b200p_stream_t stream);
 
 /* The same for the inclusive prefix sum (research/wave-primitives/benchmarks/bench_scan_dpp.hip): each wave scans its
- * 64 values `reps` times, the total fed back into the next round's inputs.  in and out: 64 * n_waves values (out
+ * 64 values `reps` times, the total fed back into the inputs of the next repetition.  in and out: 64 * n_waves values (out
  * receives the waves' final state).  backend 0: wave::dpp::scan_inclusive_sum (pair per lane); backend 1: the
  * portable shuffle-up ladder.  f32 / f64 / i32 / i64.  Throughput = 64 * n_waves * reps elements per launch. */
 int b200p_wave_scan_loop(int dtype, int backend, const void* in, void* out, int n_waves, int reps, b200p_stream_t stream);
