@@ -1070,7 +1070,14 @@ def measure(wl, args, ctx):
         t1.record()
         barrier()
     launches = pkg.launch_count() - launches0
-    ms_per_step = max_over_ranks(t0.elapsed_time(t1)) / steps
+    my_ms = t0.elapsed_time(t1)
+    ms_per_step = max_over_ranks(my_ms) / steps
+    ms_by_rank = None
+    if world > 1:                                             # every rank's own time: a straggler GPU shows here
+        mine = torch.tensor([my_ms / steps], dtype=torch.float64, device=device)
+        allr = [torch.zeros_like(mine) for _ in range(world)]
+        dist.all_gather(allr, mine)
+        ms_by_rank = [round(float(x.item()), 4) for x in allr]
     tensor_bound = getattr(wl, "bound", "hbm") == "tensor"
     unit_scale = 1e12 if tensor_bound else (1.0 if wl.unit == "tokens/s" else 1e9)
     peak = peaks["bf16_tflops"] if tensor_bound else peaks["hbm_gbs"]
@@ -1163,7 +1170,7 @@ def measure(wl, args, ctx):
                "sample": f"{wl.cpu_sample_text}, median of {n} runs of {dt:.2f} s; independent units split over {threads} host threads"}
 
     line = {"metric": wl.metric, "value": value, "unit": wl.unit, "n_gpus": world, "steps": steps,
-            "warmup": warm, "ms_per_step": ms_per_step, "higher_is_better": True,
+            "warmup": warm, "ms_per_step": ms_per_step, "ms_per_step_by_rank": ms_by_rank, "higher_is_better": True,
             "scaling": getattr(wl, "scaling", "weak"), "vs_baseline": None, "dtype": wl.dtype,
             "data": "synthetic (seeded)", "config": None, "clocks": clk.summary(), "e2e": e2e,
             "gpu_launches": launches, "roofline": roofline, "cpu_baseline": cpu, "kernels": kernels}
