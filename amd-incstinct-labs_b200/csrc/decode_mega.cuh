@@ -42,8 +42,10 @@
 // prologue, merge of the attention splits) 1 to 4 us -- they queue behind the weight prefetch that keeps
 // the memory system full -- and attention 4 to 8 us.  Five dependent exchanges per layer at 4 to 6 us
 // each leave no room under the kernel-per-phase step, whose kernel boundaries cost about the same and
-// whose launches the graph and programmatic dependent launch already overlap.  So this kernel is
-// opt-in: b200p_set_tuning("runtime_mega", 1).
+// whose launches the graph and programmatic dependent launch already overlap.  An L2 prefetch running
+// ahead of the ring's loads ("runtime_mega_ahead" stages, default 0) made it slower still: 1.03 ms per
+// token without, 1.07 / 1.08 / 1.17 at 2 / 4 / 8 stages.  So this kernel is opt-in:
+// b200p_set_tuning("runtime_mega", 1).
 // ---------------------------------------------------------------------------
 #pragma once
 #include "skinny_gemm.cuh"
