@@ -79,8 +79,13 @@ fa_step_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __rest
         dme::mbar_init(&full[0], 1); dme::mbar_init(&full[1], 1);
         dme::mbar_init_fence();
     }
-    float* q = qs + warp * D;                             // this warp's query row, read as a broadcast
-    for (int d = lane; d < D; d += 32) q[d] = to_float(Qrow[d]);
+    // This warp's query row as fp32.  With 16-bit keys a lane reads 8 floats of q per 16-byte key chunk, so the eight
+    // lanes of a shared-memory phase read pieces 32 bytes apart, 256 bytes in all: pieces 0 and 4 would share their
+    // banks.  The row is therefore stored with its float4 index f at f ^ ((f >> 3) & 1).
+    constexpr bool kSwizzleQ = sizeof(T) == 2;
+    auto qpos = [](int f4) -> int { return kSwizzleQ ? (f4 ^ ((f4 >> 3) & 1)) : f4; };
+    float* q = qs + warp * D;
+    for (int d = lane; d < D; d += 32) q[qpos(d / 4) * 4 + d % 4] = to_float(Qrow[d]);
     __syncthreads();
     if (STEP == 2 && threadIdx.x == 0) {                  // prologue: tile 0 -> buffer 0
         dme::mbar_arrive_expect_tx(&full[0], 2 * kTileBytes);
@@ -131,7 +136,7 @@ fa_step_kernel(const T* __restrict__ Q, const T* __restrict__ K, const T* __rest
                 const T* eb = reinterpret_cast<const T*>(&kb);
                 float qv[EPC];
                 #pragma unroll
-                for (int e = 0; e < EPC; e += 4) *reinterpret_cast<float4*>(&qv[e]) = *reinterpret_cast<const float4*>(q + cc * EPC + e);
+                for (int e = 0; e < EPC; e += 4) *reinterpret_cast<float4*>(&qv[e]) = *reinterpret_cast<const float4*>(q + qpos((cc * EPC + e) / 4) * 4);
                 #pragma unroll
                 for (int e = 0; e < EPC; ++e) { s0 = fmaf(qv[e], to_float(ea[e]), s0); s1 = fmaf(qv[e], to_float(eb[e]), s1); }
             }
