@@ -380,9 +380,13 @@ decode_mma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK
         dme::mbar_init_fence();
     }
     __syncthreads();
-    // Launched as a programmatic dependent (the runtime's decode step) the CTA is resident and set
-    // up by now; everything it reads from memory was produced by earlier kernels of the stream.
-    griddep_wait();
+    // Launched as a programmatic dependent (the runtime's decode step, p.pdl) the CTA is resident and set up by
+    // now, possibly while its predecessor -- the projection that writes this step's q and the cache row of the
+    // newest key -- is still running.  The key count and every cache row but the newest were written by launches
+    // that completed before the predecessor could start, so the producer reads the count and fetches the tiles
+    // that end before the newest key first, and waits for the predecessor only before the tile that holds it;
+    // the consumers wait before they touch q.
+    if (!p.pdl) griddep_wait();
     int N, per;
     decode_extent(p, N, per);
     const int k0 = min(split * per, N);
@@ -395,7 +399,9 @@ decode_mma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK
             dme::prefetch_tensor_map(&mapV);
             const uint64_t pol = dme::policy_evict_first();
             dme::Ring<STAGES> ring;
+            bool waited = !p.pdl;
             for (int t = 0; t < ntiles; ++t) {
+                if (!waited && k0 + (t + 1) * TK >= N) { griddep_wait(); waited = true; }      // this tile reaches the newest key
                 if (t >= STAGES && !dme::wait(&empty_bar[ring.stage], ring.phase ^ 1u, p.status)) { atomicExch(&s_failed, 1); break; }
                 const int key = int(p.key_offset) + k0 + t * TK;
                 unsigned char* dst = tiles + ring.stage * Sh::STAGE_BYTES;
@@ -410,6 +416,7 @@ decode_mma_kernel(const DecodeParams p, const __grid_constant__ CUtensorMap mapK
         }
     } else {
         const int g = lane / 4, t4 = lane % 4;
+        if (p.pdl) griddep_wait();                    // q comes from the predecessor
         // Q fragments: rows g and g+8 are heads of the group (zero past it)
         uint32_t qa[KS][4];
         {
