@@ -191,12 +191,33 @@ __device__ __forceinline__ void skinny_prologue(const SkinnyArgs& a, T* xs, floa
             for (int q = q0 + lane; q < q1; q += 32) *reinterpret_cast<uint2*>(dst + 4 * q) = make_uint2(0u, 0u);
         }
     } else {
-        const int vec_per_row = K / 8;                          // 16-byte vectors
-        for (int i = (warp * 32 + lane); i < Mp * vec_per_row; i += kSkinnyThreads) {
-            const int m = i / vec_per_row, v = i % vec_per_row;
-            uint4 val = make_uint4(0u, 0u, 0u, 0u);
-            if (m < a.M) val = *reinterpret_cast<const uint4*>(static_cast<const T*>(a.X16) + size_t(m) * a.ldx + size_t(v) * 8);
-            *reinterpret_cast<uint4*>(xs + size_t(m) * xstride + size_t(v) * 8) = val;
+        // 16-byte vectors, two rows at a time and up to three vectors per row and thread: the loads of a batch are all
+        // issued before its first store.  (One load and one store per trip, the stores to xs order the loads behind
+        // them: two rows of 5632 columns took six dependent trips to L2.)
+        constexpr int VB = 3;
+        const int vec_per_row = K / 8;
+        for (int m0 = 0; m0 < Mp; m0 += 2) {
+            for (int base = warp * 32 + lane; base < vec_per_row; base += kSkinnyThreads * VB) {
+                uint4 val[2][VB];
+                #pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    #pragma unroll
+                    for (int u = 0; u < VB; ++u) {
+                        const int v = base + u * kSkinnyThreads;
+                        val[r][u] = make_uint4(0u, 0u, 0u, 0u);
+                        if (m0 + r < a.M && v < vec_per_row)
+                            val[r][u] = *reinterpret_cast<const uint4*>(static_cast<const T*>(a.X16) + size_t(m0 + r) * a.ldx + size_t(v) * 8);
+                    }
+                }
+                #pragma unroll
+                for (int r = 0; r < 2; ++r) {
+                    #pragma unroll
+                    for (int u = 0; u < VB; ++u) {
+                        const int v = base + u * kSkinnyThreads;
+                        if (m0 + r < Mp && v < vec_per_row) *reinterpret_cast<uint4*>(xs + size_t(m0 + r) * xstride + size_t(v) * 8) = val[r][u];
+                    }
+                }
+            }
         }
     }
     skinny_barrier();
