@@ -622,7 +622,7 @@ __global__ void __launch_bounds__(kSkinnyStreamThreads, 1)
 decode_mega_kernel(const MegaParams p) {
     extern __shared__ __align__(128) unsigned char skinny_smem[];
     __shared__ float red[2][kSkinnyWarps][32][4];
-    __shared__ float part_ss[kSkinnyWarps];
+    __shared__ __align__(16) float part_ss[kSkinnyWarps];
     __shared__ uint64_t bars[2 * kSkinnyMaxStages];
     __shared__ unsigned long long s_keys[kMegaMaxRows];
     __shared__ int s_ids[kMegaMaxRows];
