@@ -218,3 +218,21 @@ def test_device_side_key_count_in_a_graph(b200p, torch_cuda):
         torch.cuda.synchronize()
         assert (out.float() - b200p.decode(q, K, V, N=n).float()).abs().max().item() < 1e-2, n
     assert int(n_dev.item()) == 9
+
+
+@pytest.mark.parametrize("D,N,nqh,nkvh", [(64, 640, 32, 4), (128, 384, 8, 2)])
+def test_output_that_starts_on_two_bytes(b200p, torch_cuda, D, N, nqh, nkvh):
+    """A short cache takes one split, whose result the kernel writes itself: as 16-bit pairs when the
+    output rows start on 4 bytes, one value at a time when they do not.  Both give the same bits."""
+    torch = torch_cuda
+    rng = np.random.default_rng(D + N)
+    q = dev16(torch, rng.standard_normal((2, nqh, D)).astype(np.float32) * 0.5, "bf16")
+    k = dev16(torch, rng.standard_normal((2, nkvh, N, D)).astype(np.float32) * 0.5, "bf16")
+    v = dev16(torch, rng.standard_normal((2, nkvh, N, D)).astype(np.float32) * 0.5, "bf16")
+    want = b200p.decode(q, k, v)
+    buf = torch.zeros(q.numel() + 1, dtype=q.dtype, device="cuda")
+    out = buf[1:].view(q.shape)
+    assert out.data_ptr() % 4 == 2
+    got = b200p.decode(q, k, v, out=out)
+    assert torch.equal(got, want)
+    assert float(buf[0]) == 0.0
