@@ -695,21 +695,28 @@ int launch_skinny_mh(const SkinnyArgs& a, cudaStream_t st) {
         const int x_bytes = int((smem + 127) / 128 * 128);
         int nstages = (224000 - 8192 * (MH - 1) - x_bytes) / stage_bytes;
         if (nstages > 8) nstages = 8;
+        // A few more row groups than SMs (the decode step's Q/K/V: 160 on 148), each one stage long: with one CTA per
+        // SM a dozen CTAs would take two groups one after the other and the whole grid would wait for them.  One CTA
+        // per group with a single stage instead: two of them fit an SM and run side by side.
+        const int groups_all = EPI == EPI_SILU16 ? (a.N + 7) / 8 : (a.N + 15) / 16;
+        const bool one_group_ctas = groups_all > sms && groups_all <= 2 * sms && a.K <= slab_cols &&
+                                    x_bytes + stage_bytes + 8704 * MH + 1024 <= 113 * 1024 && nstages >= 2;
+        if (one_group_ctas) nstages = 1;
         int* sticky = device_status_ptr();
         int* status = a.abort_word;
-        if (nstages >= 2 && sticky && !status) {               // no caller-owned abort word: this launch's own slot
+        if ((nstages >= 2 || one_group_ctas) && sticky && !status) {               // no caller-owned abort word: this launch's own slot
             LaunchSlot slot{};
             if (int se = take_launch_slot(st, &slot)) return se;
             status = slot.abort;
         }
-        if (nstages >= 2 && sticky) {
-            const int groups = EPI == EPI_SILU16 ? (a.N + 7) / 8 : (a.N + 15) / 16;
+        if ((nstages >= 2 || one_group_ctas) && sticky) {
+            const int groups = groups_all;
             const size_t dyn = size_t(x_bytes) + size_t(nstages) * stage_bytes;
             void (*sk)(SkinnyArgs, int, int, int*, int*) = skinny_stream_kernel<T, PRO, EPI, MH>;
             const cudaError_t ae = cudaFuncSetAttribute(sk, cudaFuncAttributeMaxDynamicSharedMemorySize, int(dyn));
             if (ae != cudaSuccess) return int(ae);
             cudaLaunchConfig_t cfg{};
-            cfg.gridDim = dim3(groups < sms ? groups : sms); cfg.blockDim = dim3(kSkinnyStreamThreads); cfg.dynamicSmemBytes = dyn; cfg.stream = st;
+            cfg.gridDim = dim3(groups < sms || one_group_ctas ? groups : sms); cfg.blockDim = dim3(kSkinnyStreamThreads); cfg.dynamicSmemBytes = dyn; cfg.stream = st;
             cudaLaunchAttribute attr[1];
             attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[0].val.programmaticStreamSerializationAllowed = 1;
