@@ -699,7 +699,8 @@ int launch_skinny_mh(const SkinnyArgs& a, cudaStream_t st) {
         // SM a dozen CTAs would take two groups one after the other and the whole grid would wait for them.  One CTA
         // per group with a single stage instead: two of them fit an SM and run side by side.
         const int groups_all = EPI == EPI_SILU16 ? (a.N + 7) / 8 : (a.N + 15) / 16;
-        const bool one_group_ctas = groups_all > sms && groups_all <= 2 * sms && a.K <= slab_cols &&
+        // (the two-fragment kernel holds too many registers for two CTAs of 288 threads on an SM)
+        const bool one_group_ctas = MH == 1 && groups_all > sms && groups_all <= 2 * sms && a.K <= slab_cols &&
                                     x_bytes + stage_bytes + 8704 * MH + 1024 <= 113 * 1024 && nstages >= 2;
         if (one_group_ctas) nstages = 1;
         int* sticky = device_status_ptr();
